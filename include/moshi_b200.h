@@ -30,7 +30,7 @@
 extern "C" {
 #endif
 
-#define B200_ABI_VERSION 4
+#define B200_ABI_VERSION 5
 
 enum {
   B200_OK = 0,
@@ -350,6 +350,26 @@ int b200_frame_read_buffer(b200_frame* f, const char* name, void* dst_dev, int64
  *           half the sum of their outputs, each RMS-normed over the width ("mix.left.out", "mix.right.out")
  *   mlp     B200_MLP_MOE_RELU2: `experts` feed-forwards W_down relu(W_up h)^2 of hidden size ff; a token uses the `top` ones
  *           with the largest router logits (fp32), weighted by the softmax over those logits alone
+ * and (the Namalix design):
+ *   block   B200_BLOCK_PARALLEL_RESIDUAL: one RMS norm whose weight is stored around zero (rms(x) * (1 + w)) feeds mixer and
+ *           feed-forward, x += mixer(h) + ff(h); the embedding is multiplied by embedding_scale; the output norm is of the same kind
+ *   mixer   B200_MIXER_SIGMOID_ATTENTION: causal attention with grouped key/value heads whose weights are
+ *           sigmoid(softcap * tanh(q.k * scale / softcap) + bias[h]) (softcap <= 0: no cap), not normalised over the keys, then
+ *           mixed over heads by an H x H matrix AFTER the sigmoid; rotary positions on the first rot_dims dimensions
+ *           (rot_pairing: halves or adjacent pairs; rot_scaling B200_ROT_RAMP: the index-ramp rescaling with an amplitude
+ *           correction on cos and sin); v_mix: the values become (1 - lambda) v + lambda v_first, v_first being the values the
+ *           first v_mix layer computed for the same token (what is cached is the blend); each head's result is multiplied by
+ *           sigmoid of a per-head gate projection
+ *           B200_MIXER_RETENTION: matrix memory with one fixed decay per head (`decay`), rotary positions on q and k, keys
+ *           scaled by dim^-1/2; the result is divided by its per-head root mean square and gated by silu(W_g h)
+ *           B200_MIXER_DELTA: the gated delta rule, S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q, behind causal
+ *           convolutions (conv_taps) with silu on q, k, v; q and k are unit vectors per head (q times dim^-1/2) shared by
+ *           heads / kv_heads value heads; beta = sigmoid(W_b h), g = exp(-exp(A_log) softplus(W_a h + dt_bias)); the result is
+ *           RMS-normed per head with one weight row and gated by silu(W_g h)
+ *   mlp     B200_MLP_DENSE_GATED_GELU: W_down (gelu_tanh(W_gate h) * (W_up h))
+ *           B200_MLP_MOE_CLAMPED_GLU: routed experts W_down (g * sigmoid(1.702 g) * (u + 1)) with g = min(W_gate h, limit),
+ *           u = clamp(W_up h, -limit, limit); router scores sigmoid(W_router h) in fp32, the `top` largest of score + correction
+ *           are chosen, weighted by score / (sum of the chosen scores) * router_scale
  * Precision: compute_dtype B200_BF16 = bf16 weights / activations / cache with fp32 accumulation, while norms, attention
  * scores and weights, gates, routers, recurrent state, the residual stream and the depth average stay fp32; B200_F32 =
  * everything in IEEE fp32 (FMA).
@@ -358,9 +378,13 @@ int b200_frame_read_buffer(b200_frame* f, const char* name, void* dst_dev, int64
  * Logits at a position do not depend on how its request was cut into steps. */
 typedef struct b200_dlm b200_dlm;
 
-enum { B200_MIXER_LATENT_ATTENTION = 1, B200_MIXER_WINDOW_ATTENTION = 2, B200_MIXER_GLA = 3, B200_MIXER_MLSTM = 4, B200_MIXER_PARALLEL = 5 };
-enum { B200_MLP_NONE = 0, B200_MLP_DENSE_RELU2 = 1, B200_MLP_MOE_RELU2 = 2 };
-enum { B200_BLOCK_GATED_DEPTH_AVERAGE = 0, B200_BLOCK_SANDWICH = 1 };
+enum { B200_MIXER_LATENT_ATTENTION = 1, B200_MIXER_WINDOW_ATTENTION = 2, B200_MIXER_GLA = 3, B200_MIXER_MLSTM = 4, B200_MIXER_PARALLEL = 5,
+       B200_MIXER_SIGMOID_ATTENTION = 6, B200_MIXER_RETENTION = 7, B200_MIXER_DELTA = 8 };
+enum { B200_MLP_NONE = 0, B200_MLP_DENSE_RELU2 = 1, B200_MLP_MOE_RELU2 = 2, B200_MLP_DENSE_GATED_GELU = 3, B200_MLP_MOE_CLAMPED_GLU = 4 };
+enum { B200_BLOCK_GATED_DEPTH_AVERAGE = 0, B200_BLOCK_SANDWICH = 1, B200_BLOCK_PARALLEL_RESIDUAL = 2 };
+enum { B200_ROT_HALVES = 0, B200_ROT_ADJACENT = 1 };          /* rot_pairing: dimension i with i + rot_dims / 2, or 2i with 2i + 1 */
+enum { B200_ROT_PLAIN = 0, B200_ROT_BANDS = 1, B200_ROT_RAMP = 2 };   /* rot_scaling */
+#define B200_DLM_MAX_DECAY_HEADS 256
 
 typedef struct {
   int kind;                   /* B200_MIXER_* (not PARALLEL)                                    */
@@ -374,6 +398,13 @@ typedef struct {
   float rot_base, rot_factor, rot_low, rot_high, rot_original;   /* rot_factor <= 0: frequencies as they are */
   float gate_cap;             /* mLSTM: cap of both gate pre-activations                        */
   float tau;                  /* GLA: decay = sigmoid(z)^(1 / tau)                              */
+  int rot_pairing;            /* B200_ROT_HALVES / B200_ROT_ADJACENT                            */
+  int rot_scaling;            /* B200_ROT_PLAIN; BANDS: rot_factor, rot_low, rot_high, rot_original (wavelength bands);
+                                 RAMP: rot_factor, rot_original, rot_fast, rot_slow (turns over rot_original positions at which the ramp starts / ends) */
+  float rot_fast, rot_slow;
+  float softcap;              /* sigmoid attention: cap of the scaled score (<= 0: none)        */
+  int v_mix;                  /* sigmoid attention: values blended with the first v_mix layer's */
+  const float* decay;         /* retention: [heads] decays (copied by create)                   */
 } b200_dlm_mixer;
 
 typedef struct {
@@ -382,6 +413,8 @@ typedef struct {
   int mlp;                    /* B200_MLP_*                                                     */
   int ff;                     /* hidden size of the feed-forward (of one expert)                */
   int experts, top;           /* routed experts and how many of them a token uses               */
+  float expert_limit;         /* clamped experts: bound of the gate (above) and of the value (both sides) */
+  float router_scale;         /* clamped experts: multiplies the normalised weights             */
 } b200_dlm_layer;
 
 typedef struct {

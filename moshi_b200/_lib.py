@@ -14,7 +14,7 @@ LIB_PATH = Path(__file__).resolve().parent / "_C" / "libmoshi_b200.so"
 
 B200_OK, B200_ERR_INVALID, B200_ERR_SHAPE, B200_ERR_STATE, B200_ERR_CUDA, B200_ERR_MISSING = range(6)
 B200_F32, B200_BF16, B200_F16, B200_I64, B200_U8, B200_I8 = range(6)
-ABI_VERSION = 4
+ABI_VERSION = 5
 
 
 class MimiConfigC(C.Structure):
@@ -45,11 +45,13 @@ class DLMMixerC(C.Structure):
     _fields_ = [("kind", C.c_int), ("heads", C.c_int), ("dim", C.c_int), ("vdim", C.c_int), ("kv_heads", C.c_int), ("kv_rank", C.c_int),
                 ("scale", C.c_float), ("window", C.c_int), ("conv_taps", C.c_int), ("rot_dims", C.c_int), ("rot_base", C.c_float),
                 ("rot_factor", C.c_float), ("rot_low", C.c_float), ("rot_high", C.c_float), ("rot_original", C.c_float),
-                ("gate_cap", C.c_float), ("tau", C.c_float)]
+                ("gate_cap", C.c_float), ("tau", C.c_float), ("rot_pairing", C.c_int), ("rot_scaling", C.c_int), ("rot_fast", C.c_float),
+                ("rot_slow", C.c_float), ("softcap", C.c_float), ("v_mix", C.c_int), ("decay", C.POINTER(C.c_float))]
 
 
 class DLMLayerC(C.Structure):
-    _fields_ = [("mixer", C.c_int), ("a", DLMMixerC), ("b", DLMMixerC), ("mlp", C.c_int), ("ff", C.c_int), ("experts", C.c_int), ("top", C.c_int)]
+    _fields_ = [("mixer", C.c_int), ("a", DLMMixerC), ("b", DLMMixerC), ("mlp", C.c_int), ("ff", C.c_int), ("experts", C.c_int), ("top", C.c_int),
+                ("expert_limit", C.c_float), ("router_scale", C.c_float)]
 
 
 class DLMConfigC(C.Structure):

@@ -269,9 +269,14 @@ def tiny_lm_config(**over) -> LMConfig:
 # ---------------------------------------------------------------------------------------------------
 # Decoder LMs given as a list of layers (text-only; no reference counterpart)
 # ---------------------------------------------------------------------------------------------------
-MIXERS = {"latent_attention": 1, "window_attention": 2, "gla": 3, "mlstm": 4, "parallel": 5}    # name -> B200_MIXER_*
-MLP_KINDS = {None: 0, "dense": 1, "moe": 2}                                                      # "mlp.kind" (or a null "mlp") -> B200_MLP_*
-BLOCKS = {"gated_depth_average": 0, "sandwich": 1}                                                # block arrangement -> B200_BLOCK_*
+MIXERS = {"latent_attention": 1, "window_attention": 2, "gla": 3, "mlstm": 4, "parallel": 5,    # name -> B200_MIXER_*
+          "sigmoid_attention": 6, "retention": 7, "delta": 8}
+# feed-forward kind -> B200_MLP_*: "dense" / "moe" are the squared-ReLU layers (a null "mlp" = none), "gated_gelu" a gated dense
+# layer with the tanh form of GELU, "moe_clamped_glu" routed experts with clamped gates behind a sigmoid router
+MLP_KINDS = {None: 0, "dense": 1, "moe": 2, "gated_gelu": 3, "moe_clamped_glu": 4}
+BLOCKS = {"gated_depth_average": 0, "sandwich": 1, "parallel_residual": 2}                        # block arrangement -> B200_BLOCK_*
+ROT_PAIRINGS = {"halves": 0, "adjacent": 1}                                                       # -> B200_ROT_HALVES / B200_ROT_ADJACENT
+ROT_SCALINGS = {None: 0, "bands": 1, "ramp": 2}                                                   # -> B200_ROT_PLAIN / BANDS / RAMP
 
 
 @dataclass
@@ -282,7 +287,11 @@ class MixerConfig:
     convolution of ``conv`` taps on the projected q / k / v, rotary positions on the first ``rot_dims`` dimensions of a head with
     base ``rot_base`` and (optionally) wavelength-dependent rescaling ``rot_scaling`` = {factor, low, high, original}.
     ``gla``: per-channel decay sigmoid(z)^(1 / tau), z through a bottleneck of ``decay_rank`` (a tensor's shape, not a config key).
-    ``mlstm``: both gate pre-activations are capped by ``gate_cap * tanh(. / gate_cap)``."""
+    ``mlstm``: both gate pre-activations are capped by ``gate_cap * tanh(. / gate_cap)``.
+    ``sigmoid_attention``: causal, weights sigmoid(softcap * tanh(q.k * scale / softcap) + bias) mixed over heads after the sigmoid;
+    ``rot_pairing`` "adjacent" turns dimension 2i with 2i + 1; ``rot_scaling_kind`` "ramp" reads ``rot_scaling`` = {factor, original,
+    fast, slow}; ``v_mix``: values blended with those of the first such layer.  ``retention``: one fixed ``decay`` per head.
+    ``delta``: gated delta rule behind convolutions of ``conv`` taps, ``kv_heads`` query/key heads shared by ``heads`` value heads."""
     kind: str
     heads: int
     dim: int
@@ -298,6 +307,11 @@ class MixerConfig:
     gate_cap: float = 0.0
     tau: float = 1.0
     decay_rank: int = 16
+    rot_pairing: str = "halves"
+    rot_scaling_kind: tp.Optional[str] = None      # None: "bands" when rot_scaling is given (the window attention's form)
+    softcap: float = 0.0
+    v_mix: bool = False
+    decay: tp.Optional[tp.List[float]] = None
 
 
 def _window_attention_from_dict(m: dict) -> MixerConfig:
@@ -331,6 +345,8 @@ class DecoderLayerConfig:
     b: tp.Optional[MixerConfig] = None
     experts: int = 0
     top: int = 0
+    expert_limit: float = 0.0
+    router_scale: float = 1.0
 
     @staticmethod
     def from_dict(d: dict) -> "DecoderLayerConfig":
@@ -489,5 +505,129 @@ class GovuvikConfig(DecoderLMConfig):
         return out
 
 
+def _rot_fields(m: dict, pairing: str) -> dict:
+    rot = m.get("rot") or {}
+    sc = rot.get("scaling")
+    return dict(rot_dims=int(rot.get("dims", 0)), rot_base=float(rot.get("base", 10000.0)), rot_scaling=dict(sc) if sc else None,
+                rot_scaling_kind="ramp" if sc else None, rot_pairing=pairing)
+
+
+def _rot_to_dict(m: MixerConfig) -> tp.Optional[dict]:
+    if m.rot_dims <= 0:
+        return None
+    rot: dict = {"base": m.rot_base, "dims": m.rot_dims}
+    if m.rot_scaling:
+        rot["scaling"] = dict(m.rot_scaling)
+    return rot
+
+
+@dataclass
+class NamalixConfig(DecoderLMConfig):
+    """``config.json`` of the Namalix design: parallel blocks (one zero-centred RMS norm feeds mixer and feed-forward,
+    ``x += mixer(h) + ff(h)``), a scaled embedding, layers of type ``attention`` (sigmoid weights mixed over heads, optional
+    blending of values with the first such layer's, a gate per head), ``retention`` (fixed decay per head) or ``delta`` (gated
+    delta rule behind short convolutions), each with a ``dense`` (gated tanh-GELU) or ``moe`` (sigmoid router with a choice
+    correction, clamped gated experts) feed-forward or none."""
+
+    TYPES = {"attention": "sigmoid_attention", "retention": "retention", "delta": "delta"}
+    FF = {"dense": "gated_gelu", "moe": "moe_clamped_glu"}
+
+    @staticmethod
+    def _layer(i: int, d: dict) -> DecoderLayerConfig:
+        t, m, mlp = d["type"], d["mixer"], d.get("mlp")
+        if t not in NamalixConfig.TYPES:
+            raise ValueError(f"layer {i}: a Namalix layer is one of {sorted(NamalixConfig.TYPES)}, not {t!r}")
+        kind = NamalixConfig.TYPES[t]
+        if t == "attention":
+            a = MixerConfig(kind=kind, heads=int(m["heads"]), kv_heads=int(m["kv_heads"]), dim=int(m["dim"]), vdim=int(m["vdim"]),
+                            scale=float(m["scale"]), softcap=float(m.get("softcap") or 0.0), v_mix=bool(m.get("v_mix", False)),
+                            **_rot_fields(m, "adjacent"))
+        elif t == "retention":
+            a = MixerConfig(kind=kind, heads=int(m["heads"]), dim=int(m["dim"]), vdim=int(m["vdim"]), decay=[float(x) for x in m["decay"]],
+                            **_rot_fields(m, "halves"))
+            if len(a.decay) != a.heads:
+                raise ValueError(f"layer {i}: retention wants one decay per head")
+        else:
+            a = MixerConfig(kind=kind, heads=int(m["heads"]), kv_heads=int(m["kv_heads"]), dim=int(m["dim"]), vdim=int(m["vdim"]),
+                            conv=int(m["conv"]))
+        if mlp is None:
+            return DecoderLayerConfig(type=kind, mlp_kind=None, a=a)
+        if mlp["kind"] not in NamalixConfig.FF:
+            raise ValueError(f"layer {i}: unknown feed-forward kind {mlp['kind']!r}")
+        if mlp["kind"] == "dense":
+            return DecoderLayerConfig(type=kind, mlp_kind="gated_gelu", ff=int(mlp["ff"]), a=a)
+        r, e = mlp["router"], mlp["expert"]
+        return DecoderLayerConfig(type=kind, mlp_kind="moe_clamped_glu", ff=int(e["ff"]), a=a, experts=int(r["experts"]), top=int(r["top"]),
+                                  expert_limit=float(e["limit"]), router_scale=float(r.get("scale", 1.0)))
+
+    @staticmethod
+    def from_dict(d: dict) -> "NamalixConfig":
+        return NamalixConfig(architecture=d["architecture"], vocab=int(d["vocab"]), width=int(d["width"]),
+                             layers=[NamalixConfig._layer(i, x) for i, x in enumerate(d["layers"])],
+                             embedding_scale=float((d.get("embedding") or {}).get("scale", 1.0)), norm_eps=float(d["norm"]["eps"]),
+                             block="parallel_residual")
+
+    @staticmethod
+    def _layer_to_dict(L: DecoderLayerConfig) -> dict:
+        a = L.a
+        if a.kind == "sigmoid_attention":
+            mixer: dict = {"dim": a.dim, "heads": a.heads, "kv_heads": a.kv_heads, "scale": a.scale, "softcap": a.softcap, "v_mix": a.v_mix, "vdim": a.vdim}
+            t = "attention"
+        elif a.kind == "retention":
+            mixer, t = {"decay": list(a.decay), "dim": a.dim, "heads": a.heads, "vdim": a.vdim}, "retention"
+        else:
+            mixer, t = {"conv": a.conv, "dim": a.dim, "heads": a.heads, "kv_heads": a.kv_heads, "vdim": a.vdim}, "delta"
+        rot = _rot_to_dict(a)
+        if rot is not None:
+            mixer["rot"] = rot
+        if L.mlp_kind is None:
+            mlp = None
+        elif L.mlp_kind == "gated_gelu":
+            mlp = {"ff": L.ff, "kind": "dense"}
+        else:
+            mlp = {"expert": {"ff": L.ff, "limit": L.expert_limit}, "kind": "moe",
+                   "router": {"experts": L.experts, "scale": L.router_scale, "top": L.top}}
+        return {"mixer": mixer, "mlp": mlp, "type": t}
+
+    def to_dict(self) -> dict:
+        return {"architecture": self.architecture, "embedding": {"scale": self.embedding_scale},
+                "layers": [self._layer_to_dict(x) for x in self.layers], "norm": {"eps": self.norm_eps}, "vocab": self.vocab, "width": self.width}
+
+    def first_v_mix_layer(self) -> int:
+        """Index of the first attention layer that blends values (its own values are the ones the later layers blend in); -1: none."""
+        for i, L in enumerate(self.layers):
+            if L.a.kind == "sigmoid_attention" and L.a.v_mix:
+                return i
+        return -1
+
+    def tensor_shapes(self) -> dict:
+        W = self.width
+        out = {"embed": (self.vocab, W)}
+        for i, L in enumerate(self.layers):
+            p, m, a = f"l{i}.", f"l{i}.mix.", L.a
+            out[p + "norm1"] = (W,)
+            if a.kind == "sigmoid_attention":
+                out.update({m + "q": (a.heads * a.dim, W), m + "k": (a.kv_heads * a.dim, W), m + "v": (a.kv_heads * a.vdim, W)})
+                if a.v_mix:
+                    out[m + "vmix"] = ()
+                out.update({m + "talk": (a.heads, a.heads), m + "pb": (a.heads,), m + "g": (a.heads, W), m + "o": (W, a.heads * a.vdim)})
+            elif a.kind == "retention":
+                out.update({m + "q": (a.heads * a.dim, W), m + "k": (a.heads * a.dim, W), m + "v": (a.heads * a.vdim, W),
+                            m + "g": (a.heads * a.vdim, W), m + "o": (W, a.heads * a.vdim)})
+            else:
+                nq, nv = a.kv_heads * a.dim, a.heads * a.vdim
+                out.update({m + "q": (nq, W), m + "q.conv": (nq, a.conv), m + "k": (nq, W), m + "k.conv": (nq, a.conv), m + "v": (nv, W),
+                            m + "v.conv": (nv, a.conv), m + "b": (a.heads, W), m + "A_log": (a.heads,), m + "norm": (a.vdim,),
+                            m + "a": (a.heads, W), m + "dt_bias": (a.heads,), m + "g": (nv, W), m + "o": (W, nv)})
+            if L.mlp_kind == "gated_gelu":
+                out.update({p + "mlp.gate": (L.ff, W), p + "mlp.up": (L.ff, W), p + "mlp.down": (W, L.ff)})
+            elif L.mlp_kind == "moe_clamped_glu":
+                for e in range(L.experts):
+                    out.update({p + f"mlp.e{e}.gate": (L.ff, W), p + f"mlp.e{e}.up": (L.ff, W), p + f"mlp.e{e}.down": (W, L.ff)})
+                out.update({p + "mlp.router": (L.experts, W), p + "mlp.correction": (L.experts,)})
+        out.update({"final.norm": (W,), "head": (self.vocab, W)})
+        return out
+
+
 # architecture name in config.json -> configuration class (the model registry of the text-only decoder LMs)
-DECODER_ARCHITECTURES: dict = {"Likosun": DecoderLMConfig, "Govuvik": GovuvikConfig}
+DECODER_ARCHITECTURES: dict = {"Likosun": DecoderLMConfig, "Govuvik": GovuvikConfig, "Namalix": NamalixConfig}

@@ -2,13 +2,15 @@
 // checkpoint's names, a slot cache per layer (latents, or keys and values, plus the carried inputs of convolutions and the
 // state of recurrent mixers), and the ragged step (any number of new tokens per slot) that both prompt portions and
 // single-token decoding go through.  Two block arrangements are registered: gated parallel sublayers with a depth-weighted
-// average (the Likosun design) and RMS-norm sandwiches around mixer and feed-forward in turn (the Govuvik design).
+// average (the Likosun design), RMS-norm sandwiches around mixer and feed-forward in turn (the Govuvik design), and a plain
+// parallel block on one zero-centred RMS norm (the Namalix design).
 #include <algorithm>
 
 #include <cmath>
 
 #include "dlm_kernels.cuh"
 #include "dlm_mixers.cuh"
+#include "dlm_mixers2.cuh"
 #include "gemm_sk.cuh"
 #include "lm_kernels.cuh"
 
@@ -51,6 +53,15 @@ struct Layer {
   Weight r_o;
   // routed experts
   void *router = nullptr, *ups = nullptr, *downs = nullptr;      // T [E][width]; T [E][ff][width]; T [E][width][ff]
+  // ---- parallel-residual block: one mixer (a) beside the feed-forward, both on the same norm.  The concatenated projection is
+  // [q | k | v | (g) | (ff gate | ff up)]; what must be fp32 before an activation (the attention's head gates, the delta rule's
+  // beta and step size, router logits) comes from one small projection w_small, T [nsmall][width]
+  int p_q = 0, p_k = 0, p_v = 0, p_g = 0, p_ffg = 0, p_ffu = 0;
+  int s_gate = 0, s_ba = 0, s_router = 0, nsmall = 0;
+  void* w_small = nullptr;
+  float *pbias = nullptr, *vlambda = nullptr, *head_decay = nullptr, *A_log = nullptr, *dt_bias = nullptr, *correction = nullptr;
+  float rot_amp = 1.f;
+  std::vector<float> decay;            // retention: the configuration's decays (copied at create)
 };
 
 // attention tile list of one (heads, rows per tile) combination
@@ -106,6 +117,11 @@ struct b200_dlm {
       *moe_tile_n = nullptr, *moe_ntiles = nullptr;
   float* sk_ws = nullptr; int* sk_counters = nullptr;
   tc::GemmPlanCache plans;
+  // parallel-residual block: recurrences that cannot run as segments (the delta rule) take the step's entries whole
+  int off_whole_tok0 = 0, off_whole_ntok = 0, off_whole_slot = 0, off_whole_pos0 = 0, off_zero = 0, off_one = 0;
+  int vmix_first = -1;                 // the first attention layer that blends values: the later ones blend its values in
+  float* small32 = nullptr;            // [tokens][nsmall] fp32 results of the small projection
+  void *vfirst = nullptr, *act2 = nullptr;      // T [tokens][G * vdim] values of layer vmix_first; T [tokens * top][2 ff] experts' first product
 };
 
 namespace {
@@ -587,37 +603,54 @@ int launch_scan_r(cudaStream_t st, const ScanParams& p, int n_entries) {
   return check_launch("matrix_memory_scan");
 }
 
-// prep rows (q, k and the decay or the two gates, fp32) for every token of the step, then the recurrence per (request, head);
-// long portions run as segments side by side, are chained, and their later segments get the carried state's share added
-template <typename T, int MODE>
-int launch_scan(b200_dlm* h, ScanParams p, int n_tok) {
-  cudaStream_t st = h->stream;
+// How the recurrence kernel is laid out for this step, set in p: 16 or 8 lanes per column, rows per thread, plain or
+// lane-ordered prep rows and their length.  whole: the step's entries are taken as they are (no segments).
+struct ScanLayout { bool wide, lanes4; int rows, nu; };
+
+template <int MODE>
+ScanLayout scan_layout(b200_dlm* h, ScanParams& p, bool whole) {
   p.prep = h->scan_prep; p.vprep = h->scan_v;
   p.vec = p.vdim % 4 == 0;
   p.stage = 8;      // short stages: less shared memory per CTA, more CTAs per SM to overlap the chains
   p.ent_par = h->meta_dev + h->off_ent_par; p.slots = h->slots;
-  p.ent_seg = h->meta_dev + h->off_ent_seg; p.ent_nseg = h->meta_dev + h->off_ent_nseg; p.ent_buf = h->meta_dev + h->off_ent_buf;
+  if (whole) {
+    p.ent_tok0 = h->meta_dev + h->off_whole_tok0; p.ent_ntok = h->meta_dev + h->off_whole_ntok; p.ent_slot = h->meta_dev + h->off_whole_slot;
+    p.ent_pos0 = h->meta_dev + h->off_whole_pos0;
+    p.ent_seg = h->meta_dev + h->off_zero; p.ent_nseg = h->meta_dev + h->off_one; p.ent_buf = h->meta_dev + h->off_zero;
+  } else {
+    p.ent_tok0 = h->meta_dev + h->off_ent_tok0; p.ent_ntok = h->meta_dev + h->off_ent_ntok; p.ent_slot = h->meta_dev + h->off_ent_slot;
+    p.ent_pos0 = h->meta_dev + h->off_ent_pos0;
+    p.ent_seg = h->meta_dev + h->off_ent_seg; p.ent_nseg = h->meta_dev + h->off_ent_nseg; p.ent_buf = h->meta_dev + h->off_ent_buf;
+  }
   p.segS = h->segS; p.segB = h->segB; p.segM = h->segM; p.qb = h->gate32; p.tokM = h->tokM;      // the decay logits are spent once prep has run
   // a few long requests: 16 lanes per column (twice the CTAs, half the chain per token); batches and single tokens: 8 lanes per
   // column (state rows read in full sectors).  Portions of more than 8 tokens: the variant whose threads own adjacent rows and
   // read q, k and the decay four rows per load from lane-ordered prep rows (a third of the instructions per token; its state
   // accesses are scattered, which costs nothing once per portion but would cost single-token steps twice their time).
-  const int nu = h->n_units;
-  const bool wide = h->max_entry_tokens > 8 && nu * p.heads * ceil_div(p.vdim, 16) < 2 * 148 && p.dim > 16;
-  const bool lanes4 = h->max_entry_tokens > 8;
-  const int lpc = wide ? 16 : 8;
-  const int rows = wide ? (p.dim <= 64 ? 4 : p.dim <= 128 ? 8 : 16) : (p.dim <= 32 ? 4 : p.dim <= 64 ? 8 : p.dim <= 128 ? 16 : 32);
-  p.lpc = lanes4 ? lpc : 0; p.rows = rows;
-  const int Dp = lanes4 ? lpc * rows : p.dim;
-  p.prow = ((MODE == MODE_DECAY ? 3 : 2) * Dp + (MODE == MODE_EXPGATE ? 2 : 0) + 3) / 4 * 4;
-  B200_LAUNCH((scan_prep_kernel<T, MODE>), n_tok, 256, 0, st, p);
-  B200_TRY(check_launch("scan_prep"));
+  ScanLayout L;
+  L.nu = whole ? h->n_entries : h->n_units;
+  L.wide = h->max_entry_tokens > 8 && L.nu * p.heads * ceil_div(p.vdim, 16) < 2 * 148 && p.dim > 16;
+  L.lanes4 = h->max_entry_tokens > 8;
+  const int lpc = L.wide ? 16 : 8;
+  L.rows = L.wide ? (p.dim <= 64 ? 4 : p.dim <= 128 ? 8 : 16) : (p.dim <= 32 ? 4 : p.dim <= 64 ? 8 : p.dim <= 128 ? 16 : 32);
+  p.lpc = L.lanes4 ? lpc : 0; p.rows = L.rows;
+  const int Dp = L.lanes4 ? lpc * L.rows : p.dim;
+  p.prow = ((MODE == MODE_DECAY ? 3 : 2) * Dp + (MODE == MODE_DECAY ? 0 : 2) + 3) / 4 * 4;
+  return L;
+}
+
+// the recurrence per (request, head) on prepared rows; long portions run as segments side by side, are chained, and their later
+// segments get the carried state's share added
+template <int MODE>
+int scan_run(b200_dlm* h, const ScanParams& p, const ScanLayout& L, bool whole) {
+  cudaStream_t st = h->stream;
+  const int nu = L.nu, rows = L.rows;
   int rc;
-  if (wide) {
+  if (L.wide) {
     if (rows == 4) rc = launch_scan_r<MODE, 4, 16, 1, true>(st, p, nu);
     else if (rows == 8) rc = launch_scan_r<MODE, 8, 16, 1, true>(st, p, nu);
     else rc = launch_scan_r<MODE, 16, 16, 1, true>(st, p, nu);
-  } else if (lanes4) {
+  } else if (L.lanes4) {
     if (rows == 4) rc = launch_scan_r<MODE, 4, 8, 1, true>(st, p, nu);
     else if (rows == 8) rc = launch_scan_r<MODE, 8, 8, 1, true>(st, p, nu);
     else if (rows == 16) rc = launch_scan_r<MODE, 16, 8, 1, true>(st, p, nu);
@@ -629,9 +662,10 @@ int launch_scan(b200_dlm* h, ScanParams p, int n_tok) {
     else rc = launch_scan_r<MODE, 32, 8, 1>(st, p, nu);
   }
   B200_TRY(rc);
+  if constexpr (MODE != MODE_DELTA) {
   bool any = false;
   for (auto& u : h->units) any |= u.buf >= 0;
-  if (!any) return B200_OK;
+  if (!any || whole) return B200_OK;
   B200_LAUNCH(scan_chain_kernel<MODE>, dim3(nu * p.heads, ceil_div((p.vdim + 1) * p.dim, 256)), 256, 0, st, p);
   B200_TRY(check_launch("scan_chain"));
   // the carried state's share for the later segments: runs of segments of one portion with equal length go as one batched product
@@ -653,15 +687,25 @@ int launch_scan(b200_dlm* h, ScanParams p, int n_tok) {
                        (int)V + 1, (int)D, (int)H, 1.f, 0, run, (long long)u.ntok * H * D, H * (V + 1) * D, (long long)u.ntok * H * (V + 1)));
       for (size_t k = i; k < j; ++k) {
         const auto& w = h->units[k];
-        const long long rows = (long long)w.ntok * H;
-        B200_LAUNCH(mlstm_combine_kernel, (unsigned)ceil_div64(rows, 4), 128, 0, st, p.out + (long long)w.tok0 * H * V, h->corr + (long long)w.tok0 * H * (V + 1),
-                    h->tokM + (long long)w.tok0 * H * 4, h->segM + (long long)w.buf * H * 4, (int)H, (int)V, rows);
+        const long long rows2 = (long long)w.ntok * H;
+        B200_LAUNCH(mlstm_combine_kernel, (unsigned)ceil_div64(rows2, 4), 128, 0, st, p.out + (long long)w.tok0 * H * V, h->corr + (long long)w.tok0 * H * (V + 1),
+                    h->tokM + (long long)w.tok0 * H * 4, h->segM + (long long)w.buf * H * 4, (int)H, (int)V, rows2);
       }
       B200_TRY(check_launch("mlstm_combine"));
     }
     i = j;
   }
+  }
   return B200_OK;
+}
+
+// prep rows (q, k and the decay or the two gates, fp32) for every token of the step, then the recurrence
+template <typename T, int MODE>
+int launch_scan(b200_dlm* h, ScanParams p, int n_tok) {
+  const ScanLayout L = scan_layout<MODE>(h, p, false);
+  B200_LAUNCH((scan_prep_kernel<T, MODE>), n_tok, 256, (size_t)2 * p.rot_half * sizeof(float), h->stream, p);
+  B200_TRY(check_launch("scan_prep"));
+  return scan_run<MODE>(h, p, L, false);
 }
 
 template <typename T>
@@ -860,6 +904,370 @@ int step_sandwich(b200_dlm* h, int n_tok, int n_want, int max_ctx, float* logits
   return check_launch("decoder LM step");
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Parallel-residual block: h = rms(x) (1 + w);  x <- x + mixer(h) + ff(h)
+// ---------------------------------------------------------------------------------------------------------------------------
+
+// rotary frequencies with the index-ramp rescaling: the index at which a wave makes t turns over `original` positions is
+// d(t) = dims ln(original / (2 pi t)) / (2 ln base); the ramp rises from 0 at lo = floor(d(fast)) to 1 at hi = ceil(d(slow));
+// f_i <- f_i / factor * ramp + f_i * (1 - ramp); cos and sin are multiplied by 0.1 ln(factor) + 1 (returned in *amp)
+std::vector<double> rotary_frequencies_ramp(const b200_dlm_mixer& m, float* amp) {
+  const int dims = m.rot_dims, half = dims / 2;
+  std::vector<double> f((size_t)std::max(half, 1), 0.0);
+  const double two_pi = 6.283185307179586476925, base = m.rot_base, orig = m.rot_original, factor = m.rot_factor;
+  auto index_of = [&](double turns) { return dims * std::log(orig / (two_pi * turns)) / (2.0 * std::log(base)); };
+  const double lo = std::max(std::floor(index_of(m.rot_fast)), 0.0), hi = std::min(std::ceil(index_of(m.rot_slow)), (double)dims - 1.0);
+  for (int i = 0; i < half; ++i) {
+    const double v = std::pow(base, -2.0 * i / dims);
+    const double ramp = std::min(std::max((i - lo) / std::max(hi - lo, 0.001), 0.0), 1.0);
+    f[i] = v / factor * ramp + v * (1.0 - ramp);
+  }
+  *amp = (float)(0.1 * std::log(factor) + 1.0);
+  return f;
+}
+
+template <typename T>
+__global__ void interleave_rows_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, long long rows, long long K) {
+  const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (i >= rows * K) return;
+  const long long r = i / K, k = i - r * K;
+  out[(2 * r) * K + k] = a[i];
+  out[(2 * r + 1) * K + k] = b[i];
+}
+
+size_t sigmoid_attn_smem(const b200_dlm_mixer& m, int QT, int KT, size_t es, int* kstride) {
+  const size_t Nq = (size_t)m.heads * m.dim, Nk = (size_t)m.kv_heads * m.dim, Nv = (size_t)m.kv_heads * m.vdim, rows = (size_t)QT * m.heads;
+  const size_t words = ((Nk * es + 3) / 4) | 1;           // an odd number of 32-bit words between staged key rows
+  *kstride = (int)(words * 4 / es);
+  return 4 * (QT * Nq + rows * m.vdim + 2 * rows * (KT + 1) + (size_t)m.heads * m.heads + m.heads) + es * ((size_t)KT * *kstride + KT * Nv) + 32;
+}
+
+int finalize_parallel_layer(b200_dlm* h, int i, std::vector<void*>& drop) {
+  Layer& L = h->layers[i];
+  const b200_dlm_config& c = h->cfg;
+  const b200_dlm_mixer& a = L.c.a;
+  const int64_t W = c.width;
+  const size_t es = esize(h);
+  const std::string p = "l" + std::to_string(i) + ".", m = p + "mix.";
+  auto matrix = [&](const std::string& name, int64_t rows, int64_t K, void** out) -> int {
+    B200_TRY(h->weights.alloc(out, (size_t)rows * K * es, false));
+    return put_matrix(h, name, rows, K, *out);
+  };
+  B200_TRY(get_f32(h, p + "norm1", W, &L.n1w));
+  B200_LAUNCH(add_one_kernel, ceil_div((int)W, 256), 256, 0, nullptr, L.n1w, (int)W);
+  const bool attn = L.c.mixer == B200_MIXER_SIGMOID_ATTENTION, ret = L.c.mixer == B200_MIXER_RETENTION, delta = L.c.mixer == B200_MIXER_DELTA;
+  const int H = a.heads, G = attn || delta ? a.kv_heads : a.heads;
+  L.Nq = (attn ? H : G) * a.dim; L.Nk = G * a.dim; L.Nv = (attn ? G : H) * a.vdim;
+  const int Ng = attn ? 0 : H * a.vdim;                    // the recurrent mixers' output gate is as wide as their result
+  const bool dense = L.c.mlp == B200_MLP_DENSE_GATED_GELU, moe = L.c.mlp == B200_MLP_MOE_CLAMPED_GLU;
+  const int F = L.c.ff, E = L.c.experts;
+  L.p_q = 0; L.p_k = L.Nq; L.p_v = L.p_k + L.Nk; L.p_g = L.p_v + L.Nv; L.p_ffg = L.p_g + Ng; L.p_ffu = L.p_ffg + (dense ? F : 0);
+  L.ncat = L.p_ffu + (dense ? F : 0);
+  L.ldp = (L.ncat + 7) / 8 * 8;
+  void* cat = nullptr;
+  B200_TRY(h->weights.alloc(&cat, (size_t)L.ncat * W * es, false));
+  auto at = [&](int off) { return static_cast<char*>(cat) + (size_t)off * W * es; };
+  B200_TRY(put_matrix(h, m + "q", L.Nq, W, at(L.p_q)));
+  B200_TRY(put_matrix(h, m + "k", L.Nk, W, at(L.p_k)));
+  B200_TRY(put_matrix(h, m + "v", L.Nv, W, at(L.p_v)));
+  if (Ng) B200_TRY(put_matrix(h, m + "g", Ng, W, at(L.p_g)));
+  if (dense) {
+    B200_TRY(put_matrix(h, p + "mlp.gate", F, W, at(L.p_ffg)));
+    B200_TRY(put_matrix(h, p + "mlp.up", F, W, at(L.p_ffu)));
+  }
+  B200_TRY(seal_weight(h, L.cat, cat, L.ncat, (int)W, drop));
+  // the small fp32 projection: head gates | beta, step size | router logits
+  L.s_gate = 0; L.s_ba = attn ? H : 0; L.s_router = L.s_ba + (delta ? 2 * H : 0); L.nsmall = L.s_router + (moe ? E : 0);
+  if (L.nsmall) {
+    B200_TRY(h->weights.alloc(&L.w_small, (size_t)L.nsmall * W * es, false));
+    auto sat = [&](int off) { return static_cast<char*>(L.w_small) + (size_t)off * W * es; };
+    if (attn) B200_TRY(put_matrix(h, m + "g", H, W, sat(L.s_gate)));
+    if (delta) {
+      B200_TRY(put_matrix(h, m + "b", H, W, sat(L.s_ba)));
+      B200_TRY(put_matrix(h, m + "a", H, W, sat(L.s_ba + H)));
+    }
+    if (moe) B200_TRY(put_matrix(h, p + "mlp.router", E, W, sat(L.s_router)));
+    h->weight_bytes += (int64_t)L.nsmall * W * es;
+  }
+  if (a.rot_dims > 0) {
+    std::vector<double> fr;
+    if (a.rot_scaling == B200_ROT_RAMP) fr = rotary_frequencies_ramp(a, &L.rot_amp);
+    else fr = rotary_frequencies(a);
+    B200_TRY(h->weights.alloc_t(&L.freq, fr.size(), false));
+    B200_CUDA(cudaMemcpy(L.freq, fr.data(), fr.size() * sizeof(double), cudaMemcpyHostToDevice));
+  }
+  if (attn) {
+    B200_TRY(get_f32_shaped(h, m + "talk", {H, H}, &L.mixhh));
+    B200_TRY(get_f32(h, m + "pb", H, &L.pbias));
+    if (a.v_mix) {
+      if (h->vmix_first < 0) h->vmix_first = i;
+      else {
+        const b200_dlm_mixer& f = h->layers[h->vmix_first].c.a;
+        if (f.kv_heads != a.kv_heads || f.vdim != a.vdim)
+          B200_FAIL(B200_ERR_SHAPE, "decoder LM: layer %d blends its values with layer %d's, whose key/value heads or value size differ", i, h->vmix_first);
+        B200_TRY(get_f32_shaped(h, m + "vmix", {}, &L.vlambda));
+      }
+    }
+    // tile of query tokens and of keys that fits shared memory
+    L.QT = 0;
+    for (int kt : {32, 16, 8}) {
+      for (int qt : {4, 2, 1}) {
+        int ks = 0;
+        const size_t sm = sigmoid_attn_smem(a, qt, kt, es, &ks);
+        if (sm <= 200 * 1024) { L.QT = qt; L.KT = kt; L.kstride = ks; L.attn_smem = sm; break; }
+      }
+      if (L.QT) break;
+    }
+    if (!L.QT) B200_FAIL(B200_ERR_SHAPE, "decoder LM: layer %d: the attention's heads do not fit shared memory", i);
+    L.sig = add_sig(h, H, L.QT * H);
+    for (int kt : {32, 16, 8}) {
+      int ks = 0;
+      const size_t sm = sigmoid_attn_smem(a, 1, kt, es, &ks);
+      if (sm <= 200 * 1024) { L.sig_one = add_sig(h, H, H); L.KT_one = kt; L.kstride_one = ks; L.smem_one = sm; break; }
+    }
+    if (!h->f32 && a.dim % 16 == 0 && a.vdim % 16 == 0) {     // bf16 cache, fragment-sized heads: the tensor-core kernel, if it fits
+      const size_t Hh = H, QS = L.Nq + 8, KS = L.Nk + 8, VS = L.Nv + 8;
+      const size_t sm = 2 * (16 * QS + 32 * KS + 32 * VS + Hh * 16 * 40) + 4 * (Hh * 16 * 40 + Hh * std::max<size_t>(Hh, 16) + Hh);
+      const int items = ceil_div(H * ceil_div(a.vdim, 64), 8);
+      if (sm <= 220 * 1024 && items <= 4) { L.sig_mma = add_sig(h, H, 16 * H); L.mma_items = items <= 2 ? items : 4; L.mma_smem = sm; }
+    }
+  } else if (ret) {
+    B200_TRY(h->weights.alloc_t(&L.head_decay, (size_t)H, false));
+    B200_CUDA(cudaMemcpy(L.head_decay, L.decay.data(), (size_t)H * sizeof(float), cudaMemcpyHostToDevice));
+  } else {
+    const int C = 2 * L.Nq + L.Nv, taps = a.conv_taps;
+    B200_TRY(h->weights.alloc_t(&L.qkv_conv, (size_t)C * taps, false));
+    const Tensor* t = nullptr;
+    int off = 0;
+    for (const char* nm : {"q", "k", "v"}) {
+      const int rows = nm[0] == 'v' ? L.Nv : L.Nq;
+      B200_TRY(find_tensor(h, m + nm + ".conv", {rows, taps}, &t));
+      B200_TRY(convert_into(t, L.qkv_conv + (size_t)off * taps));
+      off += rows;
+    }
+    h->weight_bytes += (int64_t)C * taps * 4;
+    B200_TRY(get_f32(h, m + "A_log", H, &L.A_log));
+    B200_TRY(get_f32(h, m + "dt_bias", H, &L.dt_bias));
+    B200_TRY(get_f32(h, m + "norm", a.vdim, &L.rnorm));
+  }
+  void* wo = nullptr;
+  B200_TRY(matrix(m + "o", W, (int64_t)H * a.vdim, &wo));
+  B200_TRY(seal_weight(h, L.o, wo, (int)W, H * a.vdim, drop, (int)W));
+  if (dense) {
+    void* wd = nullptr;
+    B200_TRY(matrix(p + "mlp.down", W, F, &wd));
+    B200_TRY(seal_weight(h, L.down, wd, (int)W, F, drop, (int)W));
+  } else if (moe) {
+    B200_TRY(get_f32(h, p + "mlp.correction", E, &L.correction));
+    B200_TRY(h->weights.alloc(&L.ups, (size_t)E * 2 * F * W * es, false));      // rows 2f / 2f + 1 of an expert: gate f / value f
+    B200_TRY(h->weights.alloc(&L.downs, (size_t)E * W * F * es, false));
+    void *tg = nullptr, *tu = nullptr;
+    B200_CUDA(cudaMalloc(&tg, (size_t)F * W * es));
+    B200_CUDA(cudaMalloc(&tu, (size_t)F * W * es));
+    int rc = B200_OK;
+    for (int64_t e = 0; e < E && rc == B200_OK; ++e) {
+      const std::string q = p + "mlp.e" + std::to_string(e) + ".";
+      rc = put_matrix(h, q + "gate", F, W, tg);
+      if (rc == B200_OK) rc = put_matrix(h, q + "up", F, W, tu);
+      if (rc != B200_OK) break;
+      char* dst = static_cast<char*>(L.ups) + (size_t)e * 2 * F * W * es;
+      const unsigned g = (unsigned)ceil_div64((int64_t)F * W, 256);
+      if (h->f32) interleave_rows_kernel<float><<<g, 256>>>(static_cast<const float*>(tg), static_cast<const float*>(tu), reinterpret_cast<float*>(dst), F, W);
+      else interleave_rows_kernel<bf16><<<g, 256>>>(static_cast<const bf16*>(tg), static_cast<const bf16*>(tu), reinterpret_cast<bf16*>(dst), F, W);
+      rc = check_launch("interleave_rows");
+      if (rc == B200_OK) rc = put_matrix(h, q + "down", W, F, static_cast<char*>(L.downs) + (size_t)e * W * F * es);
+    }
+    cudaDeviceSynchronize();
+    cudaFree(tg); cudaFree(tu);
+    B200_TRY(rc);
+    h->weight_bytes += 3 * (int64_t)E * F * W * es;
+  }
+  return B200_OK;
+}
+
+template <typename T>
+int sigmoid_attention(b200_dlm* h, const Layer& L, int n_tok, int max_ctx) {
+  const b200_dlm_mixer& a = L.c.a;
+  bool mma = false;
+  if constexpr (sizeof(T) == 2) mma = h->attn_tc && L.sig_mma >= 0 && (h->max_entry_tokens > 1 || h->attn_tc > 1);      // single tokens: a 16-row fragment tile would be all padding
+  const bool one = !mma && h->max_entry_tokens == 1 && L.sig_one >= 0;
+  const TileSig& s = h->sigs[mma ? L.sig_mma : one ? L.sig_one : L.sig];
+  const int QT = mma ? 16 : one ? 1 : L.QT, KT = mma ? 32 : one ? L.KT_one : L.KT;
+  static bool attr_set = false;
+  if (!attr_set) {
+    B200_CUDA(cudaFuncSetAttribute(sigmoid_attn_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    B200_CUDA(cudaFuncSetAttribute(sigmoid_attn_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+    B200_CUDA(cudaFuncSetAttribute(sigmoid_attn_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+    B200_CUDA(cudaFuncSetAttribute(sigmoid_attn_mma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+    attr_set = true;
+  }
+  SigmoidAttnParams p;
+  p.q = h->qkv32; p.ldq = L.Nq; p.kcache = L.kcache; p.vcache = L.vcache; p.mix = L.mixhh; p.bias = L.pbias;
+  p.gate_in = h->small32 + L.s_gate; p.ldg = L.nsmall;
+  p.tile_row0 = h->meta_dev + s.off_row0; p.tile_rows = h->meta_dev + s.off_rows; p.tile_slot = h->meta_dev + s.off_slot;
+  p.tok_pos = h->meta_dev + h->off_pos; p.out = h->obuf; p.part = h->part;
+  p.cap = h->cap; p.H = a.heads; p.G = a.kv_heads; p.dim = a.dim; p.vdim = a.vdim; p.QT = QT; p.KT = KT; p.kstride = one ? L.kstride_one : L.kstride;
+  p.vec = ((size_t)L.Nk * sizeof(T)) % 16 == 0 && ((size_t)L.Nv * sizeof(T)) % 16 == 0;
+  p.softcap = a.softcap;
+  // keys are cut over several CTAs per tile when the tiles alone cannot fill the GPU (decoding, short portions)
+  const int key_tiles = ceil_div(max_ctx, KT);
+  int nsplit = 1;
+  if (h->attn_split > 0) nsplit = std::min(h->attn_split, 64);
+  else if (s.count < 148) nsplit = std::min(std::max((one ? 444 : 296) / std::max(s.count, 1), 1), 64);
+  nsplit = std::max(1, std::min(nsplit, key_tiles));
+  const int rpt = QT * a.heads;
+  while (nsplit > 1 && (size_t)s.count * nsplit * rpt * a.vdim > h->part_floats) --nsplit;
+  p.nsplit = nsplit;
+  if (mma) {
+    if constexpr (sizeof(T) == 2) {
+      const dim3 grid(s.count, nsplit);
+      if (L.mma_items == 1) B200_LAUNCH(sigmoid_attn_mma_kernel<1>, grid, 256, L.mma_smem, h->stream, p);
+      else if (L.mma_items == 2) B200_LAUNCH(sigmoid_attn_mma_kernel<2>, grid, 256, L.mma_smem, h->stream, p);
+      else B200_LAUNCH(sigmoid_attn_mma_kernel<4>, grid, 256, L.mma_smem, h->stream, p);
+    }
+  } else {
+    B200_LAUNCH(sigmoid_attn_kernel<T>, dim3(s.count, nsplit), 256, one ? L.smem_one : L.attn_smem, h->stream, p);
+  }
+  B200_TRY(check_launch("sigmoid_attn"));
+  if (nsplit > 1) {
+    B200_LAUNCH(sigmoid_attn_merge_kernel<T>, dim3(s.count, rpt), 128, 0, h->stream, h->part, p.tile_row0, p.tile_rows, p.gate_in, p.ldg, static_cast<T*>(h->obuf),
+                a.heads, a.vdim, nsplit, rpt);
+    B200_TRY(check_launch("sigmoid_attn merge"));
+  }
+  return B200_OK;
+}
+
+// routed experts with clamped gates on the rows of hb -> yexp [tokens * top][W]; the router's logits are in small32
+template <typename T>
+int routed_experts_glu(b200_dlm* h, const Layer& L, const T* hb, int n_tok) {
+  const int W = h->cfg.width, E = L.c.experts, top = L.c.top, F = L.c.ff, pairs = n_tok * top;
+  cudaStream_t st = h->stream;
+  B200_LAUNCH(moe_route_sigmoid_kernel, ceil_div(n_tok, 4), 128, 0, st, h->small32 + L.s_router, (long long)L.nsmall, L.correction, E, top, L.c.router_scale,
+              h->moe_idx, h->moe_w, n_tok);
+  bool mma = false;
+  if constexpr (sizeof(T) == 2) mma = h->attn_tc && W % 16 == 0 && F % 16 == 0;
+  const int tile_m = mma ? 128 : 64;
+  B200_LAUNCH(moe_group_kernel, 1, 1024, (size_t)2 * E * sizeof(int), st, h->moe_idx, pairs, top, E, h->moe_rank, h->moe_perm, h->moe_row_tok,
+              h->moe_tile_e, h->moe_tile_r0, h->moe_tile_n, h->moe_ntiles, tile_m);
+  B200_TRY(check_launch("moe route / group"));
+  const int max_tiles = ceil_div(pairs, tile_m) + std::min(E, pairs);
+  T* act = static_cast<T*>(h->act);
+  T* act2 = static_cast<T*>(h->act2);
+  T* yexp = static_cast<T*>(h->yexp);
+  const T* ups = static_cast<const T*>(L.ups);
+  const T* downs = static_cast<const T*>(L.downs);
+  const long long n = (long long)pairs * F;
+  if (mma) {
+    if constexpr (sizeof(T) == 2) {
+      static bool attr_set = false;
+      if (!attr_set) {
+        B200_CUDA(cudaFuncSetAttribute(grouped_gemm_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GG_SMEM));
+        attr_set = true;
+      }
+      // gate and value rows of an expert are interleaved, so the first product's epilogue holds both of an output in one thread
+      B200_LAUNCH(grouped_gemm_mma_kernel, dim3(ceil_div(2 * F, 128), max_tiles), 256, GG_SMEM, st, hb, (long long)W, h->moe_row_tok, ups, (long long)W, (long long)2 * F * W,
+                  act, (long long)F, (const int*)nullptr, h->moe_tile_e, h->moe_tile_r0, h->moe_tile_n, h->moe_ntiles, 2 * F, W, 2, L.c.expert_limit);
+      B200_LAUNCH(grouped_gemm_mma_kernel, dim3(ceil_div(W, 128), max_tiles), 256, GG_SMEM, st, act, (long long)F, (const int*)nullptr, downs, (long long)F, (long long)W * F,
+                  yexp, (long long)W, h->moe_perm, h->moe_tile_e, h->moe_tile_r0, h->moe_tile_n, h->moe_ntiles, W, F, 0, 0.f);
+    }
+  } else {
+    B200_LAUNCH((grouped_gemm_kernel<T, T, T>), dim3(ceil_div(2 * F, 64), max_tiles), 256, 0, st, hb, (long long)W, h->moe_row_tok, ups, (long long)W, (long long)2 * F * W,
+                act2, (long long)2 * F, (const int*)nullptr, h->moe_tile_e, h->moe_tile_r0, h->moe_tile_n, h->moe_ntiles, 2 * F, W, 0);
+    B200_LAUNCH(clamped_glu_kernel<T>, (unsigned)ceil_div64(n, 256), 256, 0, st, act2, act, F, n, L.c.expert_limit);
+    B200_LAUNCH((grouped_gemm_kernel<T, T, T>), dim3(ceil_div(W, 64), max_tiles), 256, 0, st, act, (long long)F, (const int*)nullptr, downs, (long long)F, (long long)W * F,
+                yexp, (long long)W, h->moe_perm, h->moe_tile_e, h->moe_tile_r0, h->moe_tile_n, h->moe_ntiles, W, F, 0);
+  }
+  return check_launch("grouped expert products");
+}
+
+template <typename T>
+int step_parallel(b200_dlm* h, int n_tok, int n_want, int max_ctx, float* logits_out) {
+  const b200_dlm_config& c = h->cfg;
+  const int W = c.width;
+  cudaStream_t st = h->stream;
+  const int* meta = h->meta_dev;
+  const int *tok_slot = meta + h->off_slot, *tok_pos = meta + h->off_pos, *tok_first = meta + h->off_first, *tok_last = meta + h->off_last;
+  const long long stride = (long long)h->tmax * W;
+  T* hb = static_cast<T*>(h->hbuf);
+  T* proj = static_cast<T*>(h->proj);
+  T* ob = static_cast<T*>(h->obuf);
+  T* mixo = static_cast<T*>(h->mixo);
+  TIMED(CLS_ELEMENTWISE, B200_LAUNCH(embed_scale_norm_kernel<T>, n_tok, 256, 0, st, meta + h->off_tok, static_cast<const T*>(h->embed), c.vocab, W, c.embedding_scale,
+                                     h->layers[0].n1w, h->xin, hb, c.norm_eps, h->err));
+  for (int li = 0; li < c.n_layers; ++li) {
+    const Layer& L = h->layers[li];
+    const b200_dlm_mixer& a = L.c.a;
+    const bool last = li + 1 == c.n_layers;
+    TIMED(CLS_LINEAR, B200_TRY(linear<T>(h, hb, W, L.cat, proj, L.ldp, n_tok)));
+    if (L.nsmall) TIMED(CLS_FOLD, B200_TRY(small_proj<T>(h, hb, W, L.w_small, nullptr, h->small32, n_tok, L.nsmall, W)));
+    const int Rv = a.heads * a.vdim;
+    if (L.c.mixer == B200_MIXER_SIGMOID_ATTENTION) {
+      const bool blend = a.v_mix && li != h->vmix_first, keep = a.v_mix && li == h->vmix_first;
+      TIMED(CLS_ELEMENTWISE, B200_LAUNCH(attn_rope_cache_kernel<T>, n_tok, 256, (size_t)a.rot_dims * 4 + 4, st, proj, (long long)L.ldp, L.p_q, L.p_k, L.p_v, L.Nq, L.Nk, L.Nv,
+                                         a.dim, a.rot_dims / 2, a.rot_pairing == B200_ROT_ADJACENT, L.freq, L.rot_amp, a.scale, h->qkv32, static_cast<T*>(L.kcache),
+                                         static_cast<T*>(L.vcache), h->cap, tok_slot, tok_pos, blend ? static_cast<const T*>(h->vfirst) : (const T*)nullptr, L.vlambda,
+                                         keep ? static_cast<T*>(h->vfirst) : (T*)nullptr));
+      TIMED(CLS_ATTN, B200_TRY(sigmoid_attention<T>(h, L, n_tok, max_ctx)));
+    } else {
+      ScanParams sp;
+      sp.proj = proj; sp.ld = L.ldp; sp.off_q = L.p_q; sp.off_k = L.p_k; sp.off_v = L.p_v; sp.z = nullptr; sp.zb = nullptr;
+      sp.inv_tau = 0.f; sp.cap = 0.f; sp.St = L.St; sp.nvec = nullptr; sp.mval = nullptr;
+      sp.out = h->scan32; sp.heads = a.heads; sp.dim = a.dim; sp.vdim = a.vdim;
+      const long long rows = (long long)n_tok * a.heads;
+      if (L.c.mixer == B200_MIXER_RETENTION) {
+        sp.qscale = 1.f; sp.kscale = 1.f / sqrtf((float)a.dim); sp.head_decay = L.head_decay;
+        sp.freq = L.freq; sp.tok_pos = tok_pos; sp.rot_half = a.rot_dims / 2; sp.rot_adjacent = a.rot_pairing == B200_ROT_ADJACENT; sp.rot_amp = L.rot_amp;
+        TIMED(CLS_RECURRENT, B200_TRY((launch_scan<T, MODE_DECAY>(h, sp, n_tok))));
+        TIMED(CLS_ELEMENTWISE, B200_LAUNCH(head_norm_gate_kernel<T>, (unsigned)ceil_div64(rows, 4), 128, 0, st, h->scan32, (const float*)nullptr, 0, proj, (long long)L.ldp, L.p_g, 1, ob,
+                                           a.heads, a.vdim, rows, c.norm_eps));
+      } else {
+        const int C = 2 * L.Nq + L.Nv;
+        TIMED(CLS_ELEMENTWISE, B200_LAUNCH((causal_conv_kernel<T, float>), n_tok, 256, 0, st, proj, (long long)L.ldp, L.qkv_hist, L.qkv_conv, h->qkv32, (long long)C, C,
+                                           a.conv_taps, 0, tok_slot, tok_pos, tok_first);
+              if (a.conv_taps > 1) B200_LAUNCH(conv_carry_kernel<T>, n_tok, 256, 0, st, proj, (long long)L.ldp, L.qkv_hist, C, a.conv_taps - 1, tok_slot, tok_pos, tok_last));
+        sp.qscale = 1.f / sqrtf((float)a.dim); sp.z = h->small32 + L.s_ba;
+        const ScanLayout lay = scan_layout<MODE_DELTA>(h, sp, true);
+        TIMED(CLS_RECURRENT, B200_LAUNCH(delta_prep_kernel, n_tok, 256, (size_t)2 * a.kv_heads * sizeof(float), st, sp, h->qkv32, a.kv_heads, L.A_log, L.dt_bias, (long long)L.nsmall);
+              B200_TRY(check_launch("delta_prep"));
+              B200_TRY(scan_run<MODE_DELTA>(h, sp, lay, true)));
+        TIMED(CLS_ELEMENTWISE, B200_LAUNCH(head_norm_gate_kernel<T>, (unsigned)ceil_div64(rows, 4), 128, 0, st, h->scan32, L.rnorm, 0, proj, (long long)L.ldp, L.p_g, 1, ob,
+                                           a.heads, a.vdim, rows, c.norm_eps));
+      }
+    }
+    TIMED(CLS_LINEAR, B200_TRY(linear<T>(h, ob, (long long)Rv, L.o, mixo, W, n_tok)));
+    const T *ffo = nullptr, *yexp = nullptr;
+    if (L.c.mlp == B200_MLP_DENSE_GATED_GELU) {
+      T* act = static_cast<T*>(h->act);
+      const long long n = (long long)n_tok * L.c.ff;
+      TIMED(CLS_ELEMENTWISE, B200_LAUNCH(gated_gelu_kernel<T>, (unsigned)ceil_div64(n, 256), 256, 0, st, proj, (long long)L.ldp, L.p_ffg, L.p_ffu, act, L.c.ff, n));
+      TIMED(CLS_LINEAR, B200_TRY(linear<T>(h, act, L.c.ff, L.down, static_cast<T*>(h->ffo), W, n_tok)));
+      ffo = static_cast<const T*>(h->ffo);
+    } else if (L.c.mlp == B200_MLP_MOE_CLAMPED_GLU) {
+      TIMED(CLS_EXPERTS, B200_TRY(routed_experts_glu<T>(h, L, hb, n_tok)));
+      yexp = static_cast<const T*>(h->yexp);
+    }
+    TIMED(CLS_ELEMENTWISE, B200_LAUNCH(parallel_block_end_kernel<T>, n_tok, 256, 0, st, h->xin, mixo, ffo, yexp, h->moe_w, L.c.top,
+                                       h->trace_layers ? h->trace + (long long)li * stride : nullptr, last ? nullptr : h->layers[li + 1].n1w, hb, W, c.norm_eps));
+  }
+  B200_TRY(check_launch("decoder LM layers"));
+  if (n_want > 0) {
+    T* hf = static_cast<T*>(h->hf);
+    TIMED(CLS_ELEMENTWISE, B200_LAUNCH(rmsnorm_rows_kernel<T>, n_want, 256, 0, st, h->xin, meta + h->off_want, h->fnw, hf, W, c.norm_eps));
+    if (h->head.tiles) {
+      const int ldl = (c.vocab + 7) / 8 * 8;
+      TIMED(CLS_LINEAR, B200_TRY(linear<bf16>(h, reinterpret_cast<const bf16*>(hf), W, h->head, h->head_bf, ldl, n_want)));
+      const long long n = (long long)n_want * c.vocab;
+      B200_LAUNCH(rows_to_f32_kernel, (unsigned)ceil_div64(n, 256), 256, 0, st, h->head_bf, (long long)ldl, h->logits, c.vocab, n);
+    } else {
+      TIMED(CLS_LINEAR, B200_TRY(gemm_nt(st, hf, (long long)W, 0, static_cast<const T*>(h->head.rm), (long long)W, 0, h->logits, (long long)c.vocab, 0, n_want, c.vocab, W, 1, 1.f)));
+    }
+    if (logits_out)
+      B200_CUDA(cudaMemcpyAsync(logits_out, h->logits, (size_t)n_want * c.vocab * 4, cudaMemcpyDeviceToDevice, st));
+  }
+  return check_launch("decoder LM step");
+}
+
 }  // namespace
 
 extern "C" {
@@ -868,12 +1276,32 @@ int b200_dlm_create(const b200_dlm_config* cfg, b200_dlm** out) {
   if (!cfg || !out || !cfg->layers) B200_FAIL(B200_ERR_INVALID, "dlm_create: null argument");
   if (cfg->vocab < 1 || cfg->width < 1 || cfg->n_layers < 1) B200_FAIL(B200_ERR_INVALID, "dlm_create: vocab, width and n_layers must be positive");
   if (cfg->compute_dtype != B200_BF16 && cfg->compute_dtype != B200_F32) B200_FAIL(B200_ERR_INVALID, "dlm_create: compute_dtype must be bf16 or f32");
-  if (cfg->block != B200_BLOCK_GATED_DEPTH_AVERAGE && cfg->block != B200_BLOCK_SANDWICH) B200_FAIL(B200_ERR_INVALID, "dlm_create: unknown block arrangement %d", cfg->block);
+  if (cfg->block != B200_BLOCK_GATED_DEPTH_AVERAGE && cfg->block != B200_BLOCK_SANDWICH && cfg->block != B200_BLOCK_PARALLEL_RESIDUAL)
+    B200_FAIL(B200_ERR_INVALID, "dlm_create: unknown block arrangement %d", cfg->block);
   if (cfg->canon_taps < 0 || cfg->canon_taps > 64) B200_FAIL(B200_ERR_INVALID, "dlm_create: canon_taps must be in 0..64");
   for (int i = 0; i < cfg->n_layers; ++i) {
     const b200_dlm_layer& l = cfg->layers[i];
     const b200_dlm_mixer &a = l.a, &b = l.b;
-    if (cfg->block == B200_BLOCK_GATED_DEPTH_AVERAGE) {
+    if (cfg->block == B200_BLOCK_PARALLEL_RESIDUAL) {
+      if (a.heads < 1 || a.dim < 1 || a.vdim < 1) B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: heads, dim and vdim must be positive", i);
+      if (a.rot_dims < 0 || a.rot_dims % 2 || a.rot_dims > a.dim) B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: rot_dims must be even and at most dim", i);
+      if (a.rot_dims > 0 && a.rot_scaling == B200_ROT_RAMP && (!(a.rot_factor > 0.f) || !(a.rot_original > 0.f) || !(a.rot_fast > 0.f) || !(a.rot_slow > 0.f) || !(a.rot_base > 1.f)))
+        B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: the rotary ramp wants positive factor, original, fast and slow", i);
+      if (l.mixer == B200_MIXER_SIGMOID_ATTENTION) {
+        if (a.kv_heads < 1 || a.heads % a.kv_heads) B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: attention wants heads a multiple of kv_heads", i);
+      } else if (l.mixer == B200_MIXER_RETENTION) {
+        if (a.dim > 256 || !a.decay || a.heads > B200_DLM_MAX_DECAY_HEADS) B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: retention wants dim in 1..256 and one decay per head", i);
+      } else if (l.mixer == B200_MIXER_DELTA) {
+        if (a.dim > 256 || a.kv_heads < 1 || a.heads % a.kv_heads || a.conv_taps < 1 || a.conv_taps > 64)
+          B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: the delta rule wants dim in 1..256, heads a multiple of kv_heads and conv_taps in 1..64", i);
+      } else {
+        B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: mixer %d is not registered for this block arrangement", i, l.mixer);
+      }
+      if (l.mlp != B200_MLP_NONE && l.mlp != B200_MLP_DENSE_GATED_GELU && l.mlp != B200_MLP_MOE_CLAMPED_GLU)
+        B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: mlp kind %d is not registered for this block arrangement", i, l.mlp);
+      if (l.mlp == B200_MLP_MOE_CLAMPED_GLU && (l.experts < 1 || l.experts > 4096 || l.top < 1 || l.top > l.experts || l.top > 32 || !(l.expert_limit > 0.f)))
+        B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: experts in 1..4096, top in 1..min(experts, 32) and a positive limit", i);
+    } else if (cfg->block == B200_BLOCK_GATED_DEPTH_AVERAGE) {
       if (l.mixer != B200_MIXER_LATENT_ATTENTION) B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: mixer %d is not registered for this block arrangement", i, l.mixer);
       if (a.heads < 1 || a.dim < 1 || a.vdim < 1 || a.kv_rank < 1 || a.kv_rank > 1024)
         B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: heads, dim, vdim must be positive and kv_rank in 1..1024", i);
@@ -903,7 +1331,12 @@ int b200_dlm_create(const b200_dlm_config* cfg, b200_dlm** out) {
   auto* h = new b200_dlm();
   h->cfg = *cfg;
   h->layers.resize(cfg->n_layers);
-  for (int i = 0; i < cfg->n_layers; ++i) h->layers[i].c = cfg->layers[i];
+  for (int i = 0; i < cfg->n_layers; ++i) {
+    Layer& L = h->layers[i];
+    L.c = cfg->layers[i];
+    if (L.c.a.decay) L.decay.assign(L.c.a.decay, L.c.a.decay + L.c.a.heads);      // the caller's array does not outlive this call
+    L.c.a.decay = L.c.b.decay = nullptr;
+  }
   h->cfg.layers = nullptr;
   h->f32 = cfg->compute_dtype == B200_F32;
   if (cudaGetDevice(&h->device) != cudaSuccess) h->device = -1;
@@ -955,12 +1388,16 @@ int b200_dlm_finalize(b200_dlm* h) {
   };
   B200_TRY(matrix("embed", c.vocab, W, &h->embed));
   h->weight_bytes += (int64_t)c.vocab * W * es;
-  const bool sandwich = c.block == B200_BLOCK_SANDWICH;
+  const bool sandwich = c.block == B200_BLOCK_SANDWICH, parallel = c.block == B200_BLOCK_PARALLEL_RESIDUAL;
   if (sandwich) {
     B200_TRY(get_f32(h, "embed.norm", W, &h->embw));
     for (int i = 0; i < c.n_layers; ++i) B200_TRY(finalize_sandwich_layer(h, i, drop));
   }
-  for (int i = 0; i < c.n_layers && !sandwich; ++i) {
+  if (parallel) {
+    h->vmix_first = -1;
+    for (int i = 0; i < c.n_layers; ++i) B200_TRY(finalize_parallel_layer(h, i, drop));
+  }
+  for (int i = 0; i < c.n_layers && !sandwich && !parallel; ++i) {
     Layer& L = h->layers[i];
     const std::string p = "l" + std::to_string(i) + ".";
     const int64_t H = L.c.a.heads, dk = L.c.a.dim, dv = L.c.a.vdim, r = L.c.a.kv_rank, F = L.c.ff;
@@ -1013,7 +1450,8 @@ int b200_dlm_finalize(b200_dlm* h) {
     L.sig = sig;
   }
   B200_TRY(get_f32(h, "final.norm", W, &h->fnw));
-  if (!sandwich) B200_TRY(get_f32(h, "final.norm.b", W, &h->fnb));
+  if (parallel) B200_LAUNCH(add_one_kernel, ceil_div((int)W, 256), 256, 0, nullptr, h->fnw, (int)W);      // stored around zero
+  if (!sandwich && !parallel) B200_TRY(get_f32(h, "final.norm.b", W, &h->fnb));
   void* hd = nullptr;
   B200_TRY(matrix("head", c.vocab, W, &hd));
   B200_TRY(seal_weight(h, h->head, hd, c.vocab, (int)W, drop));
@@ -1069,13 +1507,42 @@ int b200_dlm_cache_begin(b200_dlm* h, int slots, int capacity, int max_step_toke
   const size_t es = esize(h);
   const size_t T = (size_t)max_step_tokens, W = (size_t)c.width;
   h->stream = static_cast<cudaStream_t>(stream);
-  const bool sandwich = c.block == B200_BLOCK_SANDWICH;
+  const bool sandwich = c.block == B200_BLOCK_SANDWICH, parallel = c.block == B200_BLOCK_PARALLEL_RESIDUAL;
   size_t max_ldp = 0, max_hr = 0, max_hv = 0, max_ff = 1, max_r = 0, max_tiles = 0, max_qkv = 1, max_rv = 1, max_gate = 1, max_e = 1, max_top = 0, max_part = 0, max_prep = 4, max_segrow = 1, max_heads = 1;
+  size_t max_small = 1, max_eff = 0, max_nv = 1;
   for (auto& L : h->layers) {
     const b200_dlm_mixer &a = L.c.a, &b = L.c.b;
     max_ldp = std::max(max_ldp, (size_t)L.ldp);
     max_hv = std::max(max_hv, (size_t)a.heads * a.vdim);
     max_ff = std::max(max_ff, (size_t)L.c.ff);
+    if (parallel) {
+      // per request: keys and values of an attention layer; the matrix memory of a recurrent one and its convolutions' last inputs
+      if (L.c.mixer == B200_MIXER_SIGMOID_ATTENTION) {
+        B200_TRY(A.alloc(&L.kcache, (size_t)slots * capacity * L.Nk * es));
+        B200_TRY(A.alloc(&L.vcache, (size_t)slots * capacity * L.Nv * es));
+        max_qkv = std::max(max_qkv, (size_t)L.Nq);
+        max_nv = std::max(max_nv, (size_t)L.Nv);
+        max_part = std::max(max_part, (size_t)(L.sig_mma >= 0 ? 16 : L.QT) * a.heads * a.vdim);
+      } else {
+        B200_TRY(A.alloc_t(&L.St, (size_t)slots * a.heads * a.vdim * a.dim));
+        if (L.c.mixer == B200_MIXER_DELTA) {
+          const size_t C = (size_t)2 * L.Nq + L.Nv;
+          if (a.conv_taps > 1) B200_TRY(A.alloc_t(&L.qkv_hist, (size_t)slots * (a.conv_taps - 1) * C));
+          max_qkv = std::max(max_qkv, C);
+        }
+        max_rv = std::max(max_rv, (size_t)a.heads * a.vdim);
+        max_gate = std::max(max_gate, (size_t)a.heads * a.dim);
+        max_prep = std::max(max_prep, (size_t)a.heads * (3 * (size_t)std::max(2 * a.dim, 64) + 4));
+        max_segrow = std::max(max_segrow, (size_t)a.heads * (a.vdim + 1) * a.dim);
+        max_heads = std::max(max_heads, (size_t)a.heads);
+      }
+      if (L.c.mlp == B200_MLP_MOE_CLAMPED_GLU) {
+        max_e = std::max(max_e, (size_t)L.c.experts); max_top = std::max(max_top, (size_t)L.c.top);
+        max_eff = std::max(max_eff, (size_t)L.c.top * L.c.ff);
+      }
+      max_small = std::max(max_small, (size_t)L.nsmall);
+      continue;
+    }
     if (!sandwich) {
       B200_TRY(A.alloc(&L.cache, (size_t)slots * capacity * a.kv_rank * es));
       max_hr = std::max(max_hr, (size_t)a.heads * a.kv_rank);
@@ -1111,7 +1578,38 @@ int b200_dlm_cache_begin(b200_dlm* h, int slots, int capacity, int max_step_toke
     if (L.c.mlp == B200_MLP_MOE_RELU2) { max_e = std::max(max_e, (size_t)L.c.experts); max_top = std::max(max_top, (size_t)L.c.top); }
   }
   B200_TRY(A.alloc_t(&h->xin, T * W));
-  if (!sandwich) {
+  if (parallel) {
+    const size_t nseg = (size_t)(max_step_tokens / std::max(h->scan_seg, 8) + 2);
+    B200_TRY(A.alloc_t(&h->qkv32, T * max_qkv));
+    B200_TRY(A.alloc_t(&h->small32, T * max_small));
+    B200_TRY(A.alloc_t(&h->scan32, T * max_rv));
+    B200_TRY(A.alloc_t(&h->scan_v, T * max_rv));
+    B200_TRY(A.alloc_t(&h->scan_prep, T * max_prep));
+    B200_TRY(A.alloc_t(&h->segS, nseg * max_segrow));
+    B200_TRY(A.alloc_t(&h->segB, nseg * max_gate));
+    B200_TRY(A.alloc_t(&h->segM, nseg * max_heads * 4));
+    B200_TRY(A.alloc_t(&h->tokM, T * max_heads * 4));
+    h->max_seg_units = (int)nseg;
+    B200_TRY(A.alloc_t(&h->gate32, T * max_gate));
+    B200_TRY(A.alloc(&h->ffo, T * W * es));
+    B200_TRY(A.alloc(&h->vfirst, T * max_nv * es));
+    h->part_floats = (size_t)600 * std::max(max_part, (size_t)1);
+    if (max_top) {
+      const size_t pairs = T * max_top, tiles = pairs / 64 + max_e + 2;
+      B200_TRY(A.alloc_t(&h->moe_w, pairs));
+      B200_TRY(A.alloc_t(&h->moe_idx, pairs));
+      B200_TRY(A.alloc_t(&h->moe_rank, pairs));
+      B200_TRY(A.alloc_t(&h->moe_perm, pairs));
+      B200_TRY(A.alloc_t(&h->moe_row_tok, pairs));
+      B200_TRY(A.alloc_t(&h->moe_tile_e, tiles));
+      B200_TRY(A.alloc_t(&h->moe_tile_r0, tiles));
+      B200_TRY(A.alloc_t(&h->moe_tile_n, tiles));
+      B200_TRY(A.alloc_t(&h->moe_ntiles, 1));
+      B200_TRY(A.alloc(&h->yexp, pairs * W * es));
+      B200_TRY(A.alloc(&h->act2, T * 2 * max_eff * es));
+      max_ff = std::max(max_ff, max_eff);       // the experts' hidden rows: one per (token, chosen expert)
+    }
+  } else if (!sandwich) {
     B200_TRY(A.alloc_t(&h->stack, (size_t)(c.n_layers + 1) * T * W));
     B200_TRY(A.alloc_t(&h->qa, T * max_hr));
     B200_TRY(A.alloc_t(&h->ol, T * max_hr));
@@ -1181,6 +1679,12 @@ int b200_dlm_cache_begin(b200_dlm* h, int slots, int capacity, int max_step_toke
   h->off_ent_slot = off; off += max_entries;
   h->off_ent_pos0 = off; off += max_entries;
   h->off_ent_par = off; off += max_entries;
+  h->off_whole_tok0 = off; off += max_entries;
+  h->off_whole_ntok = off; off += max_entries;
+  h->off_whole_slot = off; off += max_entries;
+  h->off_whole_pos0 = off; off += max_entries;
+  h->off_zero = off; off += max_entries;
+  h->off_one = off; off += max_entries;
   for (auto& s : h->sigs) {
     max_tiles = (size_t)ceil_div64((int64_t)max_step_tokens * s.H, s.rpt) + (size_t)std::min(slots, max_step_tokens);
     s.off_row0 = off; off += (int)max_tiles;
@@ -1249,7 +1753,7 @@ int b200_dlm_step(b200_dlm* h, int n_entries, const int32_t* slots_host, const i
       }
     }
     {   // the recurrences' units: the entry itself, or its segments when it is long
-      const int seg_len = h->scan_seg, nseg = (h->cfg.block == B200_BLOCK_SANDWICH && n >= 2 * seg_len && n_seg_units + ceil_div(n, seg_len) <= h->max_seg_units) ? ceil_div(n, seg_len) : 1;
+      const int seg_len = h->scan_seg, nseg = (h->cfg.block != B200_BLOCK_GATED_DEPTH_AVERAGE && n >= 2 * seg_len && n_seg_units + ceil_div(n, seg_len) <= h->max_seg_units) ? ceil_div(n, seg_len) : 1;
       for (int q = 0; q < nseg; ++q) {
         const int u = (int)h->units.size();
         const int u_tok0 = t + q * seg_len, u_n = nseg == 1 ? n : std::min(seg_len, n - q * seg_len);
@@ -1260,6 +1764,8 @@ int b200_dlm_step(b200_dlm* h, int n_entries, const int32_t* slots_host, const i
         if (nseg > 1) ++n_seg_units;
       }
     }
+    m[h->off_whole_tok0 + e] = t; m[h->off_whole_ntok + e] = n; m[h->off_whole_slot + e] = s; m[h->off_whole_pos0 + e] = base;
+    m[h->off_zero + e] = 0; m[h->off_one + e] = 1;
     const int first = t, lastt = t + n - 1;
     for (int i = 0; i < n; ++i, ++t) {
       m[h->off_tok + t] = tokens_host[t];
@@ -1278,7 +1784,8 @@ int b200_dlm_step(b200_dlm* h, int n_entries, const int32_t* slots_host, const i
   h->max_entry_tokens = 0;
   for (int e = 0; e < n_entries; ++e) h->max_entry_tokens = std::max(h->max_entry_tokens, (int)counts_host[e]);
   int rc;
-  if (h->cfg.block == B200_BLOCK_SANDWICH) rc = h->f32 ? step_sandwich<float>(h, t, n_want, max_ctx, logits_dev) : step_sandwich<bf16>(h, t, n_want, max_ctx, logits_dev);
+  if (h->cfg.block == B200_BLOCK_PARALLEL_RESIDUAL) rc = h->f32 ? step_parallel<float>(h, t, n_want, max_ctx, logits_dev) : step_parallel<bf16>(h, t, n_want, max_ctx, logits_dev);
+  else if (h->cfg.block == B200_BLOCK_SANDWICH) rc = h->f32 ? step_sandwich<float>(h, t, n_want, max_ctx, logits_dev) : step_sandwich<bf16>(h, t, n_want, max_ctx, logits_dev);
   else rc = h->f32 ? step_body<float>(h, t, n_want, max_ctx, logits_dev) : step_body<bf16>(h, t, n_want, max_ctx, logits_dev);
   if (rc != B200_OK) return rc;
   if (h->time_kernels && h->ev_used) {      // diagnostics only: waits for the step and sums its intervals per class
@@ -1364,6 +1871,18 @@ int64_t b200_dlm_algorithmic_bytes(b200_dlm* h, int tokens, int context) {
   if (!h) return 0;
   const int64_t es = esize(h), W = h->cfg.width;
   int64_t b = h->weight_bytes - (int64_t)h->cfg.vocab * W * es;     // the embedding is gathered, not streamed
+  if (h->cfg.block == B200_BLOCK_PARALLEL_RESIDUAL) {      // `tokens` = requests when decoding, as for the sandwich block
+    for (auto& L : h->layers) {
+      const b200_dlm_mixer& a = L.c.a;
+      if (L.c.mixer == B200_MIXER_SIGMOID_ATTENTION) b += ((int64_t)context + tokens) * (L.Nk + L.Nv) * es;      // every cached key and value once
+      else b += 2 * (int64_t)tokens * a.heads * a.dim * a.vdim * 4;                                              // the matrix memories, read and written
+      if (L.c.mlp == B200_MLP_MOE_CLAMPED_GLU) {
+        const int64_t used = std::min<int64_t>(L.c.experts, (int64_t)tokens * L.c.top);
+        b -= (int64_t)(L.c.experts - used) * 3 * L.c.ff * W * es;
+      }
+    }
+    return b + (int64_t)tokens * W * es;
+  }
   if (h->cfg.block != B200_BLOCK_SANDWICH) {
     for (auto& L : h->layers) b += ((int64_t)context + tokens) * L.c.a.kv_rank * es;
     return b + (int64_t)tokens * W * es;
@@ -1390,6 +1909,15 @@ int64_t b200_dlm_algorithmic_flops(b200_dlm* h, int tokens, int context) {
   const int64_t T = tokens, W = h->cfg.width;
   int64_t f = 0;
   for (auto& L : h->layers) {
+    if (h->cfg.block == B200_BLOCK_PARALLEL_RESIDUAL) {
+      const b200_dlm_mixer& a = L.c.a;
+      f += 2 * T * W * L.ncat + 2 * T * W * L.nsmall + 2 * T * W * a.heads * a.vdim;
+      if (L.c.mixer == B200_MIXER_SIGMOID_ATTENTION) f += 2 * a.heads * (a.dim + a.vdim + a.heads) * (T * context + T * (T + 1) / 2);      // scores, head mix, sums
+      else f += (L.c.mixer == B200_MIXER_DELTA ? 8 : 4) * T * a.heads * a.dim * a.vdim;
+      if (L.c.mlp == B200_MLP_DENSE_GATED_GELU) f += 2 * T * W * L.c.ff;                   // the down-projection (gate and value are inside ncat)
+      if (L.c.mlp == B200_MLP_MOE_CLAMPED_GLU) f += 6 * T * L.c.top * W * L.c.ff;
+      continue;
+    }
     if (h->cfg.block == B200_BLOCK_SANDWICH) {
       const b200_dlm_mixer &a = L.c.a, &m = L.c.mixer == B200_MIXER_PARALLEL ? L.c.b : L.c.a;
       f += 2 * T * W * L.ncat + 2 * T * W * m.heads * m.vdim + 4 * T * m.heads * m.dim * m.vdim;

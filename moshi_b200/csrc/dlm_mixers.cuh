@@ -551,7 +551,9 @@ __global__ void __launch_bounds__(256) small_proj_f32_kernel(const T* __restrict
 //       o_t = S^T q_t / (max(|n_t . q_t|, e^(-m_t)) + 1e-6)
 // q is scaled by qscale.  scan_prep_kernel lays out what a token contributes; matrix_memory_scan_kernel runs the recurrence.
 // ---------------------------------------------------------------------------------------------------------------------------
-enum { MODE_DECAY = 0, MODE_EXPGATE = 1 };
+//   MODE_DELTA (the gated delta rule): S <- g_t S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t
+//       (g, beta per head and token; a column of S depends on no other column, so the columns are dealt over threads as above)
+enum { MODE_DECAY = 0, MODE_EXPGATE = 1, MODE_DELTA = 2 };
 
 struct ScanParams {
   const void* proj;         // T [tokens][ld]: q at off_q, k at off_k, v at off_v (heads x dim / vdim each)
@@ -585,6 +587,13 @@ struct ScanParams {
   float* out;               // [tokens][heads * vdim]
   int heads, dim, vdim, stage, vec;      // vec: rows of prep and the 16-column slices of vprep start on 16 bytes
   int lpc = 0, rows = 0;    // lane-ordered prep rows for the kernel variant that reads four rows per load (0: plain rows)
+  // MODE_DECAY with one fixed decay per head (retention) instead of the per-channel sigmoid decay, keys scaled by kscale, and
+  // rotary positions on q and k (rot_half > 0): angle pos * freq[i], cos and sin times rot_amp, pairs by halves or adjacent
+  const float* head_decay = nullptr;
+  const double* freq = nullptr;
+  const int* tok_pos = nullptr;
+  int rot_half = 0, rot_adjacent = 0;
+  float rot_amp = 1.f, kscale = 1.f;
 };
 
 // Everything the recurrence reads, as fp32 rows that its CTAs can copy asynchronously: per (token, head)
@@ -593,8 +602,30 @@ struct ScanParams {
 // and the values as fp32.  One CTA per token.
 template <typename T, int MODE>
 __global__ void __launch_bounds__(256) scan_prep_kernel(ScanParams p) {
+  extern __shared__ float prep_rot[];   // [rot_half] cosines, [rot_half] sines of the token's position
   const long long t = blockIdx.x;
   const int heads = p.heads, dim = p.dim;
+  const int half = p.rot_half;
+  if (half > 0) {
+    const int pos = p.tok_pos[t];
+    for (int i = threadIdx.x; i < half; i += 256) {
+      double sn, cs;
+      sincos((double)pos * p.freq[i], &sn, &cs);
+      prep_rot[i] = (float)cs * p.rot_amp; prep_rot[half + i] = (float)sn * p.rot_amp;
+    }
+    __syncthreads();
+  }
+  // element d of head h of the projection at `off`, turned by the token's position when the mixer has rotary positions
+  auto turned = [&](const T* row, int off, int h, int d) -> float {
+    const T* hd = row + off + h * dim;
+    const float own = to_f(hd[d]);
+    if (d >= 2 * half) return own;
+    int i, partner; bool first;
+    if (p.rot_adjacent) { i = d >> 1; first = (d & 1) == 0; partner = d ^ 1; }
+    else { first = d < half; i = first ? d : d - half; partner = first ? d + half : d - half; }
+    const float other = to_f(hd[partner]);
+    return first ? own * prep_rot[i] - other * prep_rot[half + i] : own * prep_rot[i] + other * prep_rot[half + i];
+  };
   // plain rows (lpc = 0): q, k, a of `dim` elements each.  Lane-ordered rows (lpc > 0, for the recurrence kernel that reads four
   // rows per load): each padded with zeros to Dp = lpc * rows; lane g of a column owns rows g * rows .. g * rows + rows - 1 and
   // row g * rows + 4 c + j sits at (c * lpc + g) * 4 + j, so that a quarter-warp's 16-byte loads fall in distinct banks.
@@ -607,9 +638,12 @@ __global__ void __launch_bounds__(256) scan_prep_kernel(ScanParams p) {
     if (p.lpc > 0) { const int g = d / R, w = d - g * R; at = ((w >> 2) * p.lpc + g) * 4 + (w & 3); }
     float* o = dst + h * p.prow;
     const bool live = d < dim;
-    o[at] = live ? to_f(row[p.off_q + h * dim + d]) * p.qscale : 0.f;
-    o[Dp + at] = live ? to_f(row[p.off_k + h * dim + d]) : 0.f;
-    if (MODE == MODE_DECAY) o[2 * Dp + at] = live ? expf(log_sigmoidf(p.z[t * heads * dim + h * dim + d] + p.zb[h * dim + d]) * p.inv_tau) : 0.f;
+    o[at] = live ? turned(row, p.off_q, h, d) * p.qscale : 0.f;
+    o[Dp + at] = live ? turned(row, p.off_k, h, d) * p.kscale : 0.f;
+    if (MODE == MODE_DECAY) {
+      if (p.head_decay) o[2 * Dp + at] = live ? p.head_decay[h] : 0.f;
+      else o[2 * Dp + at] = live ? expf(log_sigmoidf(p.z[t * heads * dim + h * dim + d] + p.zb[h * dim + d]) * p.inv_tau) : 0.f;
+    }
   }
   if (MODE == MODE_EXPGATE) {
     for (int i = threadIdx.x; i < 2 * heads; i += 256) {
@@ -715,7 +749,34 @@ __global__ void __launch_bounds__(128) matrix_memory_scan_kernel(ScanParams p) {
         m = m2;
         logF += fl;
       }
-      if (VL) {
+      if (MODE == MODE_DELTA) {      // two passes over the thread's rows: decay and S^T k, then the write and the read-out
+        const float gl = aa[0], be = aa[1];
+        float dot[CB], u[CB];
+#pragma unroll
+        for (int j = 0; j < CB; ++j) dot[j] = 0.f;
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+          const int r = VL ? rg * R + i : rg + LPC * i;
+          const float kv = VL ? kk[((i >> 2) * LPC + rg) * 4 + (i & 3)] : (r < dim ? kk[r] : 0.f);
+#pragma unroll
+          for (int j = 0; j < CB; ++j) { S[i][j] *= gl; dot[j] = fmaf(S[i][j], kv, dot[j]); }
+        }
+#pragma unroll
+        for (int j = 0; j < CB; ++j) {
+#pragma unroll
+          for (int o = 1; o < LPC; o <<= 1) dot[j] += __shfl_xor_sync(0xffffffffu, dot[j], o);
+          u[j] = be * (v[j] - dot[j]);
+        }
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+          const int r = VL ? rg * R + i : rg + LPC * i;
+          const int at = VL ? ((i >> 2) * LPC + rg) * 4 + (i & 3) : r;
+          const bool live = VL || r < dim;
+          const float kv = live ? kk[at] : 0.f, qv = live ? qq[at] : 0.f;
+#pragma unroll
+          for (int j = 0; j < CB; ++j) { S[i][j] = fmaf(kv, u[j], S[i][j]); acc[j] = fmaf(S[i][j], qv, acc[j]); }
+        }
+      } else if (VL) {
 #pragma unroll
         for (int c4 = 0; c4 < R / 4; ++c4) {         // rows past dim are zeros in q, k and a: they stay zero and add nothing
           const float4 q4 = *reinterpret_cast<const float4*>(qq + (c4 * LPC + rg) * 4);
@@ -880,7 +941,7 @@ __global__ void __launch_bounds__(128) mlstm_combine_kernel(float* __restrict__ 
 }
 
 // what leaves a recurrent mixer: per head rms_norm over vdim (weight w[h * wstride + c]: wstride = 0 shares one row between
-// the heads), times a gate computed from the projection g (act 0: sigmoid, 1: silu) -> T.  One warp per (token, head).
+// the heads, w = null: no weight), times a gate computed from the projection g (act 0: sigmoid, 1: silu) -> T.  One warp per (token, head).
 template <typename T>
 __global__ void __launch_bounds__(128) head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ w, int wstride,
                                                              const T* __restrict__ proj, long long ld, int off_g, int act, T* __restrict__ out,
@@ -895,7 +956,7 @@ __global__ void __launch_bounds__(128) head_norm_gate_kernel(const float* __rest
   const float r = 1.f / sqrtf(warp_sum(s) / (float)vdim + eps);
   for (int c = lane; c < vdim; c += 32) {
     const float g = to_f(proj[t * ld + off_g + h * vdim + c]);
-    out[row * vdim + c] = from_f<T>(src[c] * r * w[(long long)h * wstride + c] * (act ? siluf(g) : sigmoidf(g)));
+    out[row * vdim + c] = from_f<T>(src[c] * r * (w ? w[(long long)h * wstride + c] : 1.f) * (act ? siluf(g) : sigmoidf(g)));
   }
 }
 
@@ -1067,7 +1128,8 @@ __global__ void __launch_bounds__(256) grouped_gemm_kernel(const TA* __restrict_
 }
 
 // The same grouped product on the tensor cores (mma.sync m16n8k16, bf16 in, fp32 accumulate): K a multiple of 16, rows of A
-// and B on 16-byte boundaries.  CTA tile 128 x 128 (tiles of 128 rows in the tile table), 8 warps of 32 x 64, 64-element
+// and B on 16-byte boundaries; act 2: gate and value rows of B alternate and the epilogue writes
+// min(g, limit) * sigmoid(1.702 min(g, limit)) * (clamp(u, -limit, limit) + 1) into column n / 2.  CTA tile 128 x 128 (tiles of 128 rows in the tile table), 8 warps of 32 x 64, 64-element
 // k-steps through two shared-memory buffers filled by cp.async (chunks outside M, N or K are zero-filled by a copy of size 0).
 __device__ __forceinline__ void cp_async_16_or_zero(void* smem_dst, const void* src, bool valid) {
   const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
@@ -1082,7 +1144,7 @@ __global__ void __launch_bounds__(256, 2) grouped_gemm_mma_kernel(const bf16* __
                                                                   const bf16* __restrict__ B, long long ldb, long long sb, bf16* __restrict__ C,
                                                                   long long ldc, const int* __restrict__ c_rows, const int* __restrict__ tile_expert,
                                                                   const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
-                                                                  const int* __restrict__ n_tiles, int N, int K, int act) {
+                                                                  const int* __restrict__ n_tiles, int N, int K, int act, float limit = 0.f) {
   constexpr int BM = GG_BM, BN = GG_BN, BK = GG_BK, ST = GG_ST;
   if ((int)blockIdx.y >= n_tiles[0]) return;
   extern __shared__ __align__(16) unsigned char gg_smem[];
@@ -1148,6 +1210,13 @@ __global__ void __launch_bounds__(256, 2) grouped_gemm_mma_kernel(const bf16* __
       for (int nb = 0; nb < 8; ++nb) {
         const int n = n0 + wn + nb * 8 + 2 * t4;
         float v0 = acc[mf][nb][2 * hf], v1 = acc[mf][nb][2 * hf + 1];
+        if (act == 2) {      // rows of B interleave gate and value: columns (n, n + 1) are one output, column n / 2 of C
+          if (n + 1 < N) {
+            const float g = fminf(v0, limit), u = fminf(fmaxf(v1, -limit), limit);
+            C[crow * ldc + (n >> 1)] = __float2bfloat16_rn(g / (1.f + expf(-1.702f * g)) * (u + 1.f));
+          }
+          continue;
+        }
         if (act) { v0 = fmaxf(v0, 0.f); v0 *= v0; v1 = fmaxf(v1, 0.f); v1 *= v1; }
         if (n + 1 < N && pair_ok) {
           *reinterpret_cast<unsigned*>(C + crow * ldc + n) = pack_bf16(v0, v1);

@@ -1,0 +1,563 @@
+// Further mechanisms of the decoder-LM handle (dlm.cu), first used by the Namalix design: a parallel block on a zero-centred
+// RMS norm, causal attention whose weights are sigmoids mixed over heads after the sigmoid (no softmax, no normaliser), rotary
+// positions on halves or on adjacent pairs with the index-ramp rescaling, values blended with those of an earlier layer, the
+// preparation of a fixed-decay retention and of the gated delta rule for the matrix-memory kernel, a gated tanh-GELU
+// feed-forward, and routed experts with clamped gates behind a sigmoid router.
+//   T = activation / weight / cache type (bf16, or float in the all-fp32 mode).  Norms, positions and angles, scores and
+//   attention weights, routers, gates, decays, unit norms, the recurrent state and the residual stream are fp32 in both modes.
+#pragma once
+
+#include "dlm_mixers.cuh"
+
+namespace b200 {
+namespace dlm {
+
+__device__ __forceinline__ float softplusf(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+__device__ __forceinline__ float gelu_tanhf(float z) { return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))); }
+// gate bounded above, value bounded on both sides: g * sigmoid(1.702 g) * (u + 1)
+__device__ __forceinline__ float clamped_gluf(float g, float u, float limit) {
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  return g * sigmoidf(1.702f * g) * (u + 1.f);
+}
+
+// x = table[token] * scale -> residual stream (fp32);  h = x / sqrt(mean(x^2) + eps) * w1 -> T   (w1 = 1 + the stored weight)
+template <typename T>
+__global__ void __launch_bounds__(256) embed_scale_norm_kernel(const int* __restrict__ tokens, const T* __restrict__ table, int vocab, int W, float scale,
+                                                               const float* __restrict__ w1, float* __restrict__ xin, T* __restrict__ h, float eps,
+                                                               int* __restrict__ err) {
+  __shared__ float red[32];
+  const long long t = blockIdx.x;
+  int id = tokens[t];
+  const bool bad = id < 0 || id >= vocab;
+  if (bad) { if (threadIdx.x == 0) atomicOr(err, ERR_TOKEN); id = 0; }
+  const T* row = table + (long long)id * W;
+  float* x = xin + t * W;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) x[i] = bad ? 0.f : to_f(row[i]) * scale;
+  __syncthreads();
+  const float r = block_rrms(x, W, eps, red);
+  for (int i = threadIdx.x; i < W; i += blockDim.x) h[t * W + i] = from_f<T>(x[i] * r * w1[i]);
+}
+
+// End of a parallel block, one CTA per token:  x <- x + mix + ff,  ff = a dense feed-forward's row | sum_k ew[t][k] * rows of
+// the chosen experts | nothing;  optional copy of x (per-layer trace);  optional h = rms_norm(x) * w_next for the next layer.
+template <typename T>
+__global__ void __launch_bounds__(256) parallel_block_end_kernel(float* __restrict__ xin, const T* __restrict__ mix, const T* __restrict__ ff,
+                                                                 const T* __restrict__ yexp, const float* __restrict__ ew, int top,
+                                                                 float* __restrict__ trace, const float* __restrict__ w_next, T* __restrict__ h,
+                                                                 int W, float eps) {
+  __shared__ float red[32];
+  const long long t = blockIdx.x;
+  float* x = xin + t * W;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    float y = to_f(mix[t * W + i]);
+    if (ff) y += to_f(ff[t * W + i]);
+    if (yexp) {
+      float acc = 0.f;
+      for (int k = 0; k < top; ++k) acc = fmaf(ew[t * top + k], to_f(yexp[(t * top + k) * W + i]), acc);
+      y += acc;
+    }
+    const float v = x[i] + y;
+    x[i] = v;
+    if (trace) trace[t * W + i] = v;
+  }
+  if (w_next) {
+    __syncthreads();
+    const float r = block_rrms(x, W, eps, red);
+    for (int i = threadIdx.x; i < W; i += blockDim.x) h[t * W + i] = from_f<T>(x[i] * r * w_next[i]);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Rotary positions.  rot[] holds, per token, cos and sin of pos * freq[i] (i < half), evaluated in double and multiplied by
+// `amp`.  Pairing B200_ROT_HALVES: dimension i turns with i + half; B200_ROT_ADJACENT: 2i with 2i + 1.  The pair (u, v) becomes
+// (u cos - v sin, v cos + u sin); dimensions from 2 * half on pass unchanged.
+// ---------------------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void rotary_fill(float* rot, int half, int pos, const double* __restrict__ freq, float amp) {
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    double sn, cs;
+    sincos((double)pos * freq[i], &sn, &cs);
+    rot[i] = (float)cs * amp; rot[half + i] = (float)sn * amp;
+  }
+}
+
+// element d of a head after rotation; `head` points at the head's first element
+template <typename T>
+__device__ __forceinline__ float rotary_at(const T* __restrict__ head, int d, int half, int adjacent, const float* __restrict__ rot) {
+  const float own = to_f(head[d]);
+  if (d >= 2 * half) return own;
+  int i, partner; bool first;
+  if (adjacent) { i = d >> 1; first = (d & 1) == 0; partner = d ^ 1; }
+  else { first = d < half; i = first ? d : d - half; partner = first ? d + half : d - half; }
+  const float other = to_f(head[partner]);
+  return first ? own * rot[i] - other * rot[half + i] : own * rot[i] + other * rot[half + i];
+}
+
+// Query / key / value preparation of the sigmoid attention, one CTA per token, on the projections proj T [tokens][ld]:
+//   q <- rope(q) * qscale -> qout fp32 [tokens][Nq];   k <- rope(k) -> key cache row;
+//   v <- (1 - lambda) v + lambda v_first (when v_first is given) -> value cache row;   v -> v_keep (when given: this layer's
+//   values are what later layers blend in).
+template <typename T>
+__global__ void __launch_bounds__(256) attn_rope_cache_kernel(const T* __restrict__ proj, long long ld, int off_q, int off_k, int off_v, int Nq, int Nk,
+                                                              int Nv, int dim, int half, int adjacent, const double* __restrict__ freq, float amp,
+                                                              float qscale, float* __restrict__ qout, T* __restrict__ kcache, T* __restrict__ vcache,
+                                                              int cap, const int* __restrict__ tok_slot, const int* __restrict__ tok_pos,
+                                                              const T* __restrict__ v_first, const float* __restrict__ lambda, T* __restrict__ v_keep) {
+  extern __shared__ float rot[];        // [half] cosines, [half] sines
+  const long long t = blockIdx.x;
+  const T* row = proj + t * ld;
+  const int pos = tok_pos[t];
+  const long long crow = (long long)tok_slot[t] * cap + pos;
+  rotary_fill(rot, half, pos, freq, amp);
+  __syncthreads();
+  for (int e = threadIdx.x; e < Nq; e += blockDim.x) {
+    const int hh = e / dim, d = e - hh * dim;
+    qout[t * Nq + e] = rotary_at(row + off_q + hh * dim, d, half, adjacent, rot) * qscale;
+  }
+  T* kc = kcache + crow * Nk;
+  for (int e = threadIdx.x; e < Nk; e += blockDim.x) {
+    const int hh = e / dim, d = e - hh * dim;
+    kc[e] = from_f<T>(rotary_at(row + off_k + hh * dim, d, half, adjacent, rot));
+  }
+  T* vc = vcache + crow * Nv;
+  const float lam = v_first ? lambda[0] : 0.f;
+  for (int e = threadIdx.x; e < Nv; e += blockDim.x) {
+    const T raw = row[off_v + e];
+    if (v_keep) v_keep[t * Nv + e] = raw;
+    vc[e] = v_first ? from_f<T>((1.f - lam) * to_f(raw) + lam * to_f(v_first[t * Nv + e])) : raw;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Causal attention with sigmoid weights and grouped keys / values.  A tile is up to QT consecutive tokens of ONE request with
+// all H query heads (the mix needs every head's weight of a (token, key) pair in one place).
+//   s[g][j]  = q_g . k_{g / (H / G)}[j]             (q carries the score scale), capped: softcap * tanh(s / softcap)
+//   w[g][j]  = sigmoid(s[g][j] + bias[g])  for keys j <= the token's position, else 0;   no normalisation over keys
+//   w'[h][j] = sum_g mix[h][g] * w[g][j]
+//   out[h]   = gate[h] * sum_j w'[h][j] v_{h / (H / G)}[j],   gate[h] = sigmoid(gate_in[token][h])
+// There is no running maximum or sum: key tiles simply add up.  nsplit > 1 (grid.y): the key tiles are dealt over the splits,
+// which leave plain partial sums per (token, head) row for sigmoid_attn_merge_kernel.
+// ---------------------------------------------------------------------------------------------------------------------------
+struct SigmoidAttnParams {
+  const float* q;           // [tokens][ldq]
+  long long ldq;
+  const void* kcache;       // T [slots][cap][G * dim]
+  const void* vcache;       // T [slots][cap][G * vdim]
+  const float* mix;         // [H][H]
+  const float* bias;        // [H]
+  const float* gate_in;     // [tokens][ldg], the H gate pre-activations first
+  long long ldg;
+  const int* tile_row0;     // first (token, head) row of the tile = first token * H
+  const int* tile_rows;     // rows of the tile = tokens * H
+  const int* tile_slot;
+  const int* tok_pos;
+  void* out;                // T [tokens][H * vdim]
+  float* part;              // nsplit > 1: [tile][split][QT * H][vdim]
+  int cap, H, G, dim, vdim, QT, KT, nsplit, kstride;      // kstride: elements between staged key rows (odd number of words)
+  int vec;                  // key and value rows are multiples of 16 bytes: staged with 16-byte loads
+  float softcap;            // <= 0: none
+};
+
+__device__ __forceinline__ float sigmoid_weight(float s, float softcap, float bias) {
+  if (softcap > 0.f) s = softcap * tanhf(s / softcap);
+  return sigmoidf(s + bias);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) sigmoid_attn_kernel(SigmoidAttnParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int H = p.H, G = p.G, dim = p.dim, vdim = p.vdim, QT = p.QT, KT = p.KT, rep = H / G;
+  const int Nq = H * dim, Nk = G * dim, Nv = G * vdim, KS = KT + 1;
+  float* qs = reinterpret_cast<float*>(smem_raw);                  // [QT][Nq]
+  float* oacc = qs + QT * Nq;                                      // [QT][H * vdim]
+  float* sw = oacc + QT * H * vdim;                                // [QT * H][KS] weights of every head
+  float* sp = sw + QT * H * KS;                                    // [QT * H][KS] mixed weights
+  float* mixs = sp + QT * H * KS;                                  // [H][H]
+  float* bs = mixs + H * H;                                        // [H]
+  T* vs = reinterpret_cast<T*>(smem_raw + (((size_t)((bs + H) - qs) * 4 + 15) / 16) * 16);     // [KT][Nv], on 16 bytes
+  T* ks = vs + (size_t)KT * Nv;                                    // [KT][kstride]
+  const int tile = blockIdx.x, split = blockIdx.y;
+  const int tok0 = p.tile_row0[tile] / H, nt = p.tile_rows[tile] / H;
+  const int p0 = p.tok_pos[tok0];                                  // positions p0 .. p0 + nt - 1
+  const T* kc = static_cast<const T*>(p.kcache) + (long long)p.tile_slot[tile] * p.cap * Nk;
+  const T* vc = static_cast<const T*>(p.vcache) + (long long)p.tile_slot[tile] * p.cap * Nv;
+  const int kmax = p0 + nt - 1;
+  const int n_kt = kmax / KT + 1;
+  const int per = (n_kt + p.nsplit - 1) / p.nsplit;
+  const int kt0 = split * per, kt1 = min(n_kt, kt0 + per);
+
+  for (int i = threadIdx.x; i < QT * Nq; i += 256) {
+    const int qt = i / Nq;
+    qs[i] = qt < nt ? p.q[(long long)(tok0 + qt) * p.ldq + (i - qt * Nq)] : 0.f;
+  }
+  for (int i = threadIdx.x; i < QT * H * vdim; i += 256) oacc[i] = 0.f;
+  for (int i = threadIdx.x; i < H * H; i += 256) mixs[i] = p.mix[i];
+  for (int i = threadIdx.x; i < H; i += 256) bs[i] = p.bias[i];
+
+  for (int kt = kt0; kt < kt1; ++kt) {
+    const int kb = kt * KT;
+    const int nk = min(KT, kmax + 1 - kb);
+    __syncthreads();
+    if (p.vec) {        // rows start on 16 bytes in the cache: 16-byte loads, 4-byte stores into the (odd-word strided) key rows
+      const int kw = Nk * (int)sizeof(T) / 16, vw = Nv * (int)sizeof(T) / 16;
+      const uint4* k4 = reinterpret_cast<const uint4*>(kc + (long long)kb * Nk);
+      const uint4* v4 = reinterpret_cast<const uint4*>(vc + (long long)kb * Nv);
+      uint32_t* ksw = reinterpret_cast<uint32_t*>(ks);
+      const int kstw = p.kstride * (int)sizeof(T) / 4;
+#pragma unroll 4
+      for (int i = threadIdx.x; i < nk * kw; i += 256) {
+        const int j = i / kw, e = i - j * kw;
+        const uint4 v = k4[i];
+        uint32_t* d = ksw + j * kstw + e * 4;
+        d[0] = v.x; d[1] = v.y; d[2] = v.z; d[3] = v.w;
+      }
+#pragma unroll 4
+      for (int i = threadIdx.x; i < nk * vw; i += 256) reinterpret_cast<uint4*>(vs)[i] = v4[i];
+    } else {
+      for (int i = threadIdx.x; i < nk * Nk; i += 256) { const int j = i / Nk, e = i - j * Nk; ks[j * p.kstride + e] = kc[(long long)(kb + j) * Nk + e]; }
+      for (int i = threadIdx.x; i < nk * Nv; i += 256) vs[i] = vc[(long long)kb * Nv + i];
+    }
+    __syncthreads();
+    // weights of every head: item (row = qt * H + g, key j), keys fastest
+    for (int i = threadIdx.x; i < QT * H * KT; i += 256) {
+      const int row = i / KT, j = i - row * KT;
+      const int qt = row / H, g = row - qt * H;
+      float w = 0.f;
+      if (j < nk && qt < nt && kb + j <= p0 + qt) {
+        const float* qv = qs + qt * Nq + g * dim;
+        const T* kv = ks + j * p.kstride + (g / rep) * dim;
+        float acc = 0.f;
+        for (int d = 0; d < dim; ++d) acc = fmaf(qv[d], to_f(kv[d]), acc);
+        w = sigmoid_weight(acc, p.softcap, bs[g]);
+      }
+      sw[row * KS + j] = w;
+    }
+    __syncthreads();
+    // mix over heads (a key the token does not see has weight 0 in every head, so the mix leaves it 0)
+    for (int i = threadIdx.x; i < nt * H * KT; i += 256) {
+      const int row = i / KT, j = i - row * KT;
+      const int qt = row / H, h = row - qt * H;
+      float s = 0.f;
+      for (int g = 0; g < H; ++g) s = fmaf(mixs[h * H + g], sw[(qt * H + g) * KS + j], s);
+      sp[row * KS + j] = s;
+    }
+    __syncthreads();
+    // weighted sum of the values: item (row, c), c fastest
+    for (int i = threadIdx.x; i < nt * H * vdim; i += 256) {
+      const int row = i / vdim, c = i - row * vdim;
+      const T* vv = vs + ((row % H) / rep) * vdim + c;
+      const float* w = sp + row * KS;
+      float acc = oacc[i];
+      for (int j = 0; j < nk; ++j) acc = fmaf(w[j], to_f(vv[j * Nv]), acc);
+      oacc[i] = acc;
+    }
+  }
+  __syncthreads();
+  if (p.nsplit == 1) {
+    T* out = static_cast<T*>(p.out);
+    for (int i = threadIdx.x; i < nt * H * vdim; i += 256) {
+      const int row = i / vdim;
+      const float gate = sigmoidf(p.gate_in[(long long)(tok0 + row / H) * p.ldg + row % H]);
+      out[(long long)tok0 * H * vdim + i] = from_f<T>(oacc[i] * gate);
+    }
+  } else {
+    float* dst = p.part + ((long long)tile * p.nsplit + split) * (QT * H) * vdim;
+    for (int i = threadIdx.x; i < nt * H * vdim; i += 256) dst[i] = oacc[i];
+  }
+}
+
+// sums the key splits of one (token, head) row in split order and applies the head's gate; grid (tiles, rows per tile)
+template <typename T>
+__global__ void __launch_bounds__(128) sigmoid_attn_merge_kernel(const float* __restrict__ part, const int* __restrict__ tile_row0,
+                                                                 const int* __restrict__ tile_rows, const float* __restrict__ gate_in, long long ldg,
+                                                                 T* __restrict__ out, int H, int vdim, int nsplit, int rows_per_tile) {
+  const int tile = blockIdx.x, lr = blockIdx.y;
+  if (lr >= tile_rows[tile]) return;
+  const long long row = tile_row0[tile] + lr;
+  const float gate = sigmoidf(gate_in[(row / H) * ldg + row % H]);
+  const float* base = part + ((long long)tile * nsplit * rows_per_tile + lr) * vdim;
+  const long long ss = (long long)rows_per_tile * vdim;
+  for (int c = threadIdx.x; c < vdim; c += 128) {
+    float acc = 0.f;
+    for (int s = 0; s < nsplit; ++s) acc += base[s * ss + c];
+    out[row * vdim + c] = from_f<T>(acc * gate);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// The same attention on the tensor cores for bf16 caches (dim and vdim multiples of 16): a tile is 16 consecutive tokens of one
+// request with all H heads, a key tile 32 keys.  Per key tile: (1) scores Q_g K^T per head as mma.sync m16n8k16 (queries rounded
+// to bf16 once, fp32 accumulate), cap, bias and sigmoid in fp32 on the accumulator registers, weights into shared memory as
+// fp32; (2) the mix over heads in fp32, one warp per token, lane = key, the mixed weights going back as bf16; (3) O_h += W'_h V
+// on the tensor cores, the accumulators of a warp's NI items (head, 64 value columns) in registers.
+// ---------------------------------------------------------------------------------------------------------------------------
+template <int NI>
+__global__ void __launch_bounds__(256) sigmoid_attn_mma_kernel(SigmoidAttnParams p) {
+  constexpr int QT = 16, KT = 32, SS = 40, PS = 40;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int H = p.H, G = p.G, dim = p.dim, vdim = p.vdim, rep = H / G;
+  const int Nq = H * dim, Nk = G * dim, Nv = G * vdim, QS = Nq + 8, KS = Nk + 8, VS = Nv + 8, VC = (vdim + 63) / 64;
+  bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                   // [16][QS]
+  bf16* Ks = Qs + QT * QS;                                        // [32][KS]
+  bf16* Vs = Ks + KT * KS;                                        // [32][VS]
+  bf16* pb = Vs + KT * VS;                                        // [H][16][PS] mixed weights of the key tile
+  float* sw = reinterpret_cast<float*>(pb + H * QT * PS);         // [H][16][SS] weights of every head
+  float* mixs = sw + H * QT * SS;                                 // [H][max(H, 16)]
+  float* bs = mixs + H * max(H, 16);                              // [H]
+  const int tile = blockIdx.x, split = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g8 = lane >> 2, t4 = lane & 3, mi = lane >> 3;
+  const int tok0 = p.tile_row0[tile] / H, nt = p.tile_rows[tile] / H;
+  const int p0 = p.tok_pos[tok0];
+  const bf16* kc = static_cast<const bf16*>(p.kcache) + (long long)p.tile_slot[tile] * p.cap * Nk;
+  const bf16* vc = static_cast<const bf16*>(p.vcache) + (long long)p.tile_slot[tile] * p.cap * Nv;
+  const int kmax = p0 + nt - 1;
+  const int n_kt = kmax / KT + 1;
+  const int per = (n_kt + p.nsplit - 1) / p.nsplit;
+  const int kt0 = split * per, kt1 = min(n_kt, kt0 + per);
+
+  for (int i = threadIdx.x; i < QT * (Nq / 2); i += 256) {
+    const int qt = i / (Nq / 2), e = (i - qt * (Nq / 2)) * 2;
+    float2 v = make_float2(0.f, 0.f);
+    if (qt < nt) v = *reinterpret_cast<const float2*>(p.q + (long long)(tok0 + qt) * p.ldq + e);
+    *reinterpret_cast<unsigned*>(Qs + qt * QS + e) = pack_bf16(v.x, v.y);
+  }
+  if (H <= 16) {      // rows padded to 16 entries (zeros) for the register-blocked mix
+    for (int i = threadIdx.x; i < H * 16; i += 256) mixs[i] = (i & 15) < H ? p.mix[(i >> 4) * H + (i & 15)] : 0.f;
+  } else {
+    for (int i = threadIdx.x; i < H * H; i += 256) mixs[i] = p.mix[i];
+  }
+  for (int i = threadIdx.x; i < H; i += 256) bs[i] = p.bias[i];
+  float oacc[NI][8][4];
+#pragma unroll
+  for (int a = 0; a < NI; ++a)
+#pragma unroll
+    for (int b = 0; b < 8; ++b) { oacc[a][b][0] = oacc[a][b][1] = oacc[a][b][2] = oacc[a][b][3] = 0.f; }
+
+  for (int kt = kt0; kt < kt1; ++kt) {
+    const int kb = kt * KT;
+    const int nk = min(KT, kmax + 1 - kb);
+    __syncthreads();
+    {   // keys and values of the tile: 16-byte loads; rows past the last key are zero (their weights are zero, they must be finite)
+      const int kw = Nk / 8, vw = Nv / 8;
+      const uint4* k4 = reinterpret_cast<const uint4*>(kc + (long long)kb * Nk);
+      const uint4* v4 = reinterpret_cast<const uint4*>(vc + (long long)kb * Nv);
+#pragma unroll 4
+      for (int i = threadIdx.x; i < KT * kw; i += 256) {
+        const int j = i / kw, e = i - j * kw;
+        *reinterpret_cast<uint4*>(Ks + j * KS + e * 8) = j < nk ? k4[i] : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll 4
+      for (int i = threadIdx.x; i < KT * vw; i += 256) {
+        const int j = i / vw, e = i - j * vw;
+        *reinterpret_cast<uint4*>(Vs + j * VS + e * 8) = j < nk ? v4[i] : make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+    __syncthreads();
+    // (1) scores and weights, one head at a time per warp
+    for (int h = warp; h < H; h += 8) {
+      const bf16* qh = Qs + h * dim;
+      const bf16* kh = Ks + (h / rep) * dim;
+      float sacc[4][4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { sacc[i][0] = sacc[i][1] = sacc[i][2] = sacc[i][3] = 0.f; }
+      for (int ks = 0; ks < dim / 16; ++ks) {
+        unsigned a[4];
+        ldmatrix_x4(a, qh + ((mi & 1) * 8 + (lane & 7)) * QS + ks * 16 + (mi >> 1) * 8);
+#pragma unroll
+        for (int np = 0; np < 2; ++np) {
+          unsigned b[4];
+          ldmatrix_x4(b, kh + (np * 16 + (mi >> 1) * 8 + (lane & 7)) * KS + ks * 16 + (mi & 1) * 8);
+          mma_bf16_16816(sacc[2 * np], a, b[0], b[1]);
+          mma_bf16_16816(sacc[2 * np + 1], a, b[2], b[3]);
+        }
+      }
+      float* dst = sw + h * QT * SS;
+      const float bias = bs[h];
+#pragma unroll
+      for (int nb = 0; nb < 4; ++nb) {
+        const int j = nb * 8 + 2 * t4;      // keys j, j + 1 of the tile; rows g8 and g8 + 8
+        float w[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int qt = g8 + 8 * (e >> 1), kj = kb + j + (e & 1);
+          const bool vis = j + (e & 1) < nk && qt < nt && kj <= p0 + qt;
+          w[e] = vis ? sigmoid_weight(sacc[nb][e], p.softcap, bias) : 0.f;
+        }
+        *reinterpret_cast<float2*>(dst + g8 * SS + j) = make_float2(w[0], w[1]);
+        *reinterpret_cast<float2*>(dst + (g8 + 8) * SS + j) = make_float2(w[2], w[3]);
+      }
+    }
+    __syncthreads();
+    // (2) mix over heads; lane = key
+    if (H <= 16) {
+      for (int qt = warp; qt < QT; qt += 8) {
+        float raw[16];
+#pragma unroll
+        for (int g = 0; g < 16; ++g) raw[g] = g < H ? sw[(g * QT + qt) * SS + lane] : 0.f;
+        for (int h = 0; h < H; ++h) {
+          const float4* mr = reinterpret_cast<const float4*>(mixs + h * 16);
+          float s = 0.f;
+#pragma unroll
+          for (int g4 = 0; g4 < 4; ++g4) {
+            const float4 mv = mr[g4];
+            s = fmaf(mv.x, raw[4 * g4], s); s = fmaf(mv.y, raw[4 * g4 + 1], s); s = fmaf(mv.z, raw[4 * g4 + 2], s); s = fmaf(mv.w, raw[4 * g4 + 3], s);
+          }
+          pb[(h * QT + qt) * PS + lane] = __float2bfloat16_rn(s);
+        }
+      }
+    } else {
+      for (int row = warp; row < H * QT; row += 8) {
+        const int h = row / QT, qt = row - h * QT;
+        float s = 0.f;
+        for (int g = 0; g < H; ++g) s = fmaf(mixs[h * H + g], sw[(g * QT + qt) * SS + lane], s);
+        pb[row * PS + lane] = __float2bfloat16_rn(s);
+      }
+    }
+    __syncthreads();
+    // (3) weighted sums of the values
+#pragma unroll
+    for (int ii = 0; ii < NI; ++ii) {
+      const int it = warp + 8 * ii;
+      if (it >= H * VC) break;
+      const int h = it / VC, c0 = (it - h * VC) * 64;
+      const bf16* vh = Vs + (h / rep) * vdim + c0;
+#pragma unroll
+      for (int k2 = 0; k2 < 2; ++k2) {
+        unsigned pf[4];
+        ldmatrix_x4(pf, pb + h * QT * PS + ((lane & 7) + 8 * ((lane >> 3) & 1)) * PS + 16 * k2 + 8 * (lane >> 4));
+#pragma unroll
+        for (int np = 0; np < 4; ++np) {
+          if (c0 + np * 16 < vdim) {
+            unsigned b[4];
+            ldmatrix_x4_trans(b, vh + (k2 * 16 + (mi & 1) * 8 + (lane & 7)) * VS + np * 16 + (mi >> 1) * 8);
+            mma_bf16_16816(oacc[ii][2 * np], pf, b[0], b[1]);
+            mma_bf16_16816(oacc[ii][2 * np + 1], pf, b[2], b[3]);
+          }
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int ii = 0; ii < NI; ++ii) {
+    const int it = warp + 8 * ii;
+    if (it >= H * VC) break;
+    const int h = it / VC, c0 = (it - h * VC) * 64;
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      const int qt = g8 + 8 * hf;
+      if (qt >= nt) continue;
+      if (p.nsplit == 1) {
+        const float gate = sigmoidf(p.gate_in[(long long)(tok0 + qt) * p.ldg + h]);
+        bf16* dst = static_cast<bf16*>(p.out) + ((long long)(tok0 + qt) * H + h) * vdim + c0;
+#pragma unroll
+        for (int nb = 0; nb < 8; ++nb)
+          if (c0 + nb * 8 < vdim)
+            *reinterpret_cast<unsigned*>(dst + nb * 8 + 2 * t4) = pack_bf16(oacc[ii][nb][2 * hf] * gate, oacc[ii][nb][2 * hf + 1] * gate);
+      } else {
+        float* dst = p.part + (((long long)tile * p.nsplit + split) * (QT * H) + qt * H + h) * vdim;
+#pragma unroll
+        for (int nb = 0; nb < 8; ++nb)
+          if (c0 + nb * 8 < vdim)
+            *reinterpret_cast<float2*>(dst + c0 + nb * 8 + 2 * t4) = make_float2(oacc[ii][nb][2 * hf], oacc[ii][nb][2 * hf + 1]);
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Preparation of the gated delta rule for matrix_memory_scan_kernel<MODE_DELTA>, one CTA per token, on the convolved projections
+// c fp32 [tokens][2 * G * dim + heads * vdim] (q, k, v before their activation):
+//   q <- unit(silu(q)) * dim^-1/2,  k <- unit(silu(k))   per query/key head, unit(x) = x / sqrt(sum x^2 + 1e-6);
+//   value head h reads query/key head h / (heads / G);   v <- silu(v);
+//   beta = sigmoid(z[h]),  g = exp(-exp(A_log[h]) * softplus(z[heads + h] + dt_bias[h]))   (z: the two gate projections, fp32)
+// prep row of (token, head): [q | k | g, beta] (plain or lane-ordered, as scan_prep_kernel lays rows out).
+// ---------------------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) delta_prep_kernel(ScanParams p, const float* __restrict__ conv, int G, const float* __restrict__ A_log,
+                                                         const float* __restrict__ dt_bias, long long ldz) {
+  extern __shared__ float rinv[];       // [2 * G] inverse lengths of the q and k heads
+  const long long t = blockIdx.x;
+  const int heads = p.heads, dim = p.dim, vdim = p.vdim, rep = heads / G;
+  const int C = 2 * G * dim + heads * vdim;
+  const float* c = conv + t * C;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int u = warp; u < 2 * G; u += 8) {
+    float s = 0.f;
+    for (int d = lane; d < dim; d += 32) { const float v = siluf(c[u * dim + d]); s += v * v; }
+    s = warp_sum(s);
+    if (lane == 0) rinv[u] = 1.f / sqrtf(s + 1e-6f);
+  }
+  __syncthreads();
+  const int R = p.rows, Dp = p.lpc > 0 ? p.lpc * p.rows : dim;
+  float* dst = p.prep + t * heads * p.prow;
+  for (int i = threadIdx.x; i < heads * Dp; i += 256) {
+    const int h = i / Dp, d = i - h * Dp, g = h / rep;
+    int at = d;
+    if (p.lpc > 0) { const int gg = d / R, w = d - gg * R; at = ((w >> 2) * p.lpc + gg) * 4 + (w & 3); }
+    float* o = dst + h * p.prow;
+    const bool live = d < dim;
+    o[at] = live ? siluf(c[g * dim + d]) * rinv[g] * p.qscale : 0.f;
+    o[Dp + at] = live ? siluf(c[(G + g) * dim + d]) * rinv[G + g] : 0.f;
+  }
+  for (int h = threadIdx.x; h < heads; h += 256) {
+    const float* z = p.z + t * ldz;
+    dst[h * p.prow + 2 * Dp] = expf(-expf(A_log[h]) * softplusf(z[heads + h] + dt_bias[h]));
+    dst[h * p.prow + 2 * Dp + 1] = sigmoidf(z[h]);
+  }
+  for (int i = threadIdx.x; i < heads * vdim; i += 256) p.vprep[t * heads * vdim + i] = siluf(c[2 * G * dim + i]);
+}
+
+// out = gelu_tanh(gate) * up on the two halves of a concatenated projection
+template <typename T>
+__global__ void __launch_bounds__(256) gated_gelu_kernel(const T* __restrict__ proj, long long ldp, int off_gate, int off_up, T* __restrict__ out, int F, long long n) {
+  const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (i >= n) return;
+  const long long t = i / F; const int f = (int)(i - t * F);
+  out[i] = from_f<T>(gelu_tanhf(to_f(proj[t * ldp + off_gate + f])) * to_f(proj[t * ldp + off_up + f]));
+}
+
+// out[r][f] = clamped_glu(in[r][2f], in[r][2f + 1]): the experts' first product with gate and value rows interleaved
+template <typename T>
+__global__ void __launch_bounds__(256) clamped_glu_kernel(const T* __restrict__ in, T* __restrict__ out, int F, long long n, float limit) {
+  const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (i >= n) return;
+  const long long r = i / F; const int f = (int)(i - r * F);
+  out[i] = from_f<T>(clamped_gluf(to_f(in[r * 2 * F + 2 * f]), to_f(in[r * 2 * F + 2 * f + 1]), limit));
+}
+
+// Router with sigmoid scores, per token (one warp): s = sigmoid(logit); the `top` experts with the largest s + correction are
+// chosen (ties: the lower index); their weights are s / (sum of the chosen s + 1e-20) * out_scale.
+__global__ void __launch_bounds__(128) moe_route_sigmoid_kernel(const float* __restrict__ logits, long long ldl, const float* __restrict__ correction,
+                                                                int E, int top, float out_scale, int* __restrict__ idx, float* __restrict__ wts, int n_tok) {
+  const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (t >= n_tok) return;
+  const float* z = logits + (long long)t * ldl;
+  float den = 0.f;
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY, bs = 0.f; int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      bool taken = false;
+      for (int j = 0; j < k; ++j) taken |= idx[(long long)t * top + j] == e;
+      const float s = sigmoidf(z[e]), v = s + correction[e];
+      if (!taken && (v > best || (v == best && e < bi))) { best = v; bi = e; bs = s; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o), os = __shfl_xor_sync(0xffffffffu, bs, o); const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; bs = os; }
+    }
+    den += bs;
+    if (lane == 0) { idx[(long long)t * top + k] = bi; wts[(long long)t * top + k] = bs; }
+    __syncwarp();
+  }
+  __syncwarp();
+  if (lane < top) wts[(long long)t * top + lane] = wts[(long long)t * top + lane] / (den + 1e-20f) * out_scale;
+}
+
+// w <- 1 + w (a norm weight stored around zero), once at load
+__global__ void add_one_kernel(float* __restrict__ w, int n) {
+  const int i = blockIdx.x * 256 + threadIdx.x;
+  if (i < n) w[i] += 1.f;
+}
+
+}  // namespace dlm
+}  // namespace b200

@@ -12,7 +12,7 @@ import typing as tp
 import torch
 
 from .. import _lib
-from ..config import BLOCKS, MIXERS, MLP_KINDS, DecoderLMConfig, MixerConfig
+from ..config import BLOCKS, MIXERS, MLP_KINDS, ROT_PAIRINGS, ROT_SCALINGS, DecoderLMConfig, MixerConfig
 
 _DTYPES = {torch.bfloat16: _lib.B200_BF16, torch.float32: _lib.B200_F32}
 
@@ -23,6 +23,12 @@ def _fill_mixer(dst, m: MixerConfig) -> None:
     sc = m.rot_scaling or {}
     dst.rot_factor, dst.rot_low, dst.rot_high = float(sc.get("factor", 0.0)), float(sc.get("low", 1.0)), float(sc.get("high", 1.0))
     dst.rot_original, dst.gate_cap, dst.tau = float(sc.get("original", 0.0)), m.gate_cap, m.tau
+    dst.rot_pairing = ROT_PAIRINGS[m.rot_pairing]
+    dst.rot_scaling = ROT_SCALINGS[m.rot_scaling_kind if m.rot_scaling else None] if m.rot_scaling_kind else (1 if m.rot_scaling else 0)
+    dst.rot_fast, dst.rot_slow = float(sc.get("fast", 0.0)), float(sc.get("slow", 0.0))
+    dst.softcap, dst.v_mix = m.softcap, int(m.v_mix)
+    if m.decay:
+        dst.decay = (C.c_float * len(m.decay))(*m.decay)      # ctypes keeps the array alive with the struct; create() copies it
 
 
 class DecoderLM:
@@ -46,6 +52,7 @@ class DecoderLM:
         for i, L in enumerate(cfg.layers):
             layers[i].mixer, layers[i].mlp, layers[i].ff = MIXERS[L.type], MLP_KINDS[L.mlp_kind], L.ff
             layers[i].experts, layers[i].top = L.experts, L.top
+            layers[i].expert_limit, layers[i].router_scale = L.expert_limit, L.router_scale
             for dst, m in zip((layers[i].a, layers[i].b), L.mixers()):
                 if m is not None:
                     _fill_mixer(dst, m)
