@@ -275,10 +275,21 @@ def iter_synth_decoder_tensors(cfg: DecoderLMConfig, seed: int = 99, device="cpu
     sit around 1, biases and sinks around 0, and the depth-average rows are positive and sum to 1, so that activations keep a
     sane scale through any number of layers."""
     gen = _gen(seed, device)
+    zero_centred = cfg.block == "parallel_residual"          # norm weights stored around zero (the norm multiplies by 1 + w)
     for name, shape in cfg.tensor_shapes().items():
         leaf = name.split(".", 1)[-1] if name.startswith("l") and name[1].isdigit() else name
         last = leaf.rsplit(".", 1)[-1]
-        if leaf in ("norm1", "final.norm", "mix.dkv.norm") or (len(shape) == 1 and last in ("norm", "norm1b", "norm2", "norm2b", "out")):
+        if zero_centred and leaf in ("norm1", "final.norm"):
+            t = _uniform(gen, shape, 0.2, device)
+        elif last == "vmix":            # how much of the first blending layer's values a later one takes
+            t = 0.3 + _uniform(gen, shape, 0.2, device)
+        elif last == "pb":              # sigmoid weights are not normalised over keys: start them small
+            t = -2.0 + _uniform(gen, shape, 0.5, device)
+        elif last == "A_log":           # delta rule: decays near one
+            t = -1.5 + _uniform(gen, shape, 0.5, device)
+        elif last in ("dt_bias", "correction"):
+            t = _uniform(gen, shape, 0.3, device)
+        elif leaf in ("norm1", "final.norm", "mix.dkv.norm") or (len(shape) == 1 and last in ("norm", "norm1b", "norm2", "norm2b", "out")):
             t = 1.0 + _uniform(gen, shape, 0.2, device)
         elif last == "temp":
             t = 1.0 + _uniform(gen, shape, 0.3, device)
