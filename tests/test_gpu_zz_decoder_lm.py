@@ -343,7 +343,7 @@ def write_model(folder, cfg, tensors):
     (folder / "config.json").write_text(json.dumps(cfg.to_dict()))
     header, data = {}, b""
     for k, t in tensors.items():
-        raw = t.contiguous().view(torch.uint8).numpy().tobytes()
+        raw = t.contiguous().reshape(-1).view(torch.uint8).numpy().tobytes()      # reshape: a scalar has no axis to view as bytes
         header[k] = {"dtype": "BF16", "shape": list(t.shape), "data_offsets": [len(data), len(data) + len(raw)]}
         data += raw
     hj = json.dumps(header).encode()
