@@ -786,6 +786,109 @@ def govuvik_arm(args) -> None:
     print(json.dumps(out))
 
 
+# ---------------------------------------------------------------------------------------------
+# --decoder-lm --decoder-arch namalix: the Namalix design beside the Govuvik decoder LM (the closest existing model: attention beside
+# recurrent matrix memories and routed experts on the same handle and step) at equal width, depth, head shapes, experts and vocabulary
+# ---------------------------------------------------------------------------------------------
+NAMALIX_SIZES = {
+    # name: (width, layer types, attention heads, kv heads, head dim, recurrent heads, key dim, value dim, experts, top, expert ff, dense ff, vocab)
+    "w2048": (2048, ("delta", "attention", "retention", "attention"), 16, 4, 128, 8, 128, 256, 16, 2, 4096, 8192, 32000),
+    "w4096": (4096, ("delta", "attention"), 16, 4, 128, 16, 128, 256, 16, 2, 8192, 16384, 32000),
+}
+
+
+def _namalix_cfg(size: str):
+    from moshi_b200.config import DecoderLMConfig
+    W, kinds, H, G, d, Hr, dk, dv, E, top, ff, dff, V = NAMALIX_SIZES[size]
+    moe = {"expert": {"ff": ff, "limit": 7.0}, "kind": "moe", "router": {"experts": E, "scale": 2.5, "top": top}}
+    mixers = {
+        "attention": {"dim": d, "heads": H, "kv_heads": G, "scale": d ** -0.5, "softcap": 30.0, "v_mix": True, "vdim": d,
+                      "rot": {"base": 500000.0, "dims": d // 2, "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}},
+        "retention": {"decay": [1.0 - 2.0 ** (-5 - 5 * i / max(Hr - 1, 1)) for i in range(Hr)], "dim": dk, "heads": Hr, "vdim": dv, "rot": {"base": 1000000.0, "dims": dk}},
+        "delta": {"conv": 4, "dim": dk, "heads": Hr, "kv_heads": Hr, "vdim": dv},
+    }
+    layers = [{"type": k, "mixer": mixers[k], "mlp": {"ff": dff, "kind": "dense"} if i == 0 else moe} for i, k in enumerate(kinds)]
+    return DecoderLMConfig.from_dict({"architecture": "Namalix", "embedding": {"scale": W ** 0.5}, "norm": {"eps": 1e-6}, "vocab": V, "width": W, "layers": layers})
+
+
+def namalix_arm(args) -> None:
+    """Prefill (one prompt of --prefill-tokens) and decode (--decode-batch requests, one token each, on --context cached tokens)
+    of the Namalix design with random weights, per size, whole steps and per class of kernel against the measured rooflines; the
+    Govuvik numbers of the same width and depth come from `--decoder-lm --decoder-arch govuvik`."""
+    from moshi_b200 import _lib
+    from moshi_b200.models import DecoderLMGen, loaders
+    device = torch.device("cuda:0")
+    torch.cuda.set_device(device)
+    hbm, src = _peaks()
+    pk = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+    tf = float(pk.get("bf16_tflops", 1590.0))
+    T, B, ctx = args.prefill_tokens, args.decode_batch, args.context
+    g = torch.Generator().manual_seed(7)
+    out = {"impl": "b200", "mode": "decoder-lm", "arch": "namalix", "dtype": "bf16", "data": "synthetic (random weights)",
+           "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "source": src}, "workload": {"prefill_tokens": T, "decode_batch": B, "context": ctx}, "sizes": {}}
+    launches0 = _lib.lib().b200_launch_count()
+    for size in args.decoder_sizes.split(","):
+        cfg = _namalix_cfg(size)
+        W, kinds, H, G, d, Hr, dk, dv, E, top, ff, dff, V = NAMALIX_SIZES[size]
+        n_attn, n_ret, n_delta, n_moe = kinds.count("attention"), kinds.count("retention"), kinds.count("delta"), len(kinds) - 1
+        model = loaders.get_decoder_lm(None, cfg, device=device, synth_seed=11)
+        res = {"config": dict(zip(("width", "layers", "heads", "kv_heads", "head_dim", "recurrent_heads", "key_dim", "value_dim", "experts", "top",
+                                   "expert_ff", "dense_ff", "vocab"), NAMALIX_SIZES[size]))}
+        gen = DecoderLMGen(model, slots=B, capacity=ctx + 64, max_step_tokens=max(T, B), max_want=B)
+        prompt = torch.randint(0, V, (T,), generator=g).tolist()
+
+        def prefill():
+            gen.step([(0, prompt)], [T - 1])
+            gen.release(0)
+        ms = _timed_steps(prefill, args.steps, args.warmup)
+        gen.set_option("time_kernels", 1)
+        gen.kernel_times()
+        for _ in range(3):
+            prefill()
+        kt = {k: v / 3 for k, v in gen.kernel_times().items()}
+        gen.set_option("time_kernels", 0)
+        fl = model.algorithmic_flops(T, 0)
+        pairs = T * (T + 1) // 2
+        attn_fl = 2 * pairs * H * 2 * d * n_attn                  # the two products on the tensor cores (the head mix runs beside them in fp32)
+        exp_fl = 6 * T * top * W * ff * n_moe
+        rec_fl = 4 * T * Hr * dk * dv * (n_ret + 2 * n_delta)
+        lin_fl = fl - 2 * pairs * H * (2 * d + H) * n_attn - exp_fl - rec_fl
+        res["prefill"] = {"ms": ms, "tokens_per_s": T / ms * 1e3, "tflops": fl / ms / 1e9, "frac_of_bf16_peak": fl / ms / 1e9 / tf, "kernel_ms": kt,
+                          "kernel_frac_of_bf16_peak": {"linear": lin_fl / kt["linear"] / 1e9 / tf, "attention": attn_fl / kt["attention"] / 1e9 / tf,
+                                                       "experts": exp_fl / kt["experts"] / 1e9 / tf, "recurrent": rec_fl / kt["recurrent"] / 1e9 / tf}}
+        filler = torch.randint(0, V, (ctx,), generator=g).tolist()
+        for b in range(B):
+            for a in range(0, ctx, max(T, B)):
+                gen.step([(b, filler[a:a + max(T, B)])], [])
+        toks = torch.randint(0, V, (B,), generator=g).tolist()
+
+        def decode():
+            gen.step([(b, [toks[b]]) for b in range(B)], list(range(B)))
+        n_dec = min(args.steps, 40)
+        ms = _timed_steps(decode, n_dec, min(args.warmup, 5))
+        gen.set_option("time_kernels", 1)
+        gen.kernel_times()
+        for _ in range(3):
+            decode()
+        kt = {k: v / 3 for k, v in gen.kernel_times().items()}
+        gen.set_option("time_kernels", 0)
+        nbytes = model.algorithmic_bytes(B, B * ctx)
+        attn_bytes = B * ctx * 2 * G * d * 2 * n_attn
+        rec_bytes = 2 * B * Hr * dk * dv * 4 * (n_ret + n_delta)
+        exp_bytes = min(E, B * top) * 3 * ff * W * 2 * n_moe
+        lin_bytes = nbytes - attn_bytes - rec_bytes - exp_bytes
+        res["decode"] = {"ms": ms, "tokens_per_s": B / ms * 1e3, "algorithmic_bytes": nbytes, "frac_of_hbm_peak": nbytes / ms / 1e6 / hbm, "kernel_ms": kt,
+                         "kernel_frac_of_hbm_peak": {"linear": lin_bytes / kt["linear"] / 1e6 / hbm, "attention": attn_bytes / kt["attention"] / 1e6 / hbm,
+                                                     "recurrent": rec_bytes / kt["recurrent"] / 1e6 / hbm, "experts": exp_bytes / kt["experts"] / 1e6 / hbm}}
+        assert gen.error_flags() == 0
+        gen.close()
+        del gen, model
+        torch.cuda.empty_cache()
+        out["sizes"][size] = res
+    out["gpu_launches"] = int(_lib.lib().b200_launch_count() - launches0)
+    print(json.dumps(out))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -803,15 +906,16 @@ def main() -> None:
     ap.add_argument("--decoder-lm", action="store_true",
                     help="instead of the default workload: prefill / decode throughput of the text-only decoder LM (Likosun design, random "
                          "weights) beside the Moshi temporal transformer at equal width and depth; prints its own JSON line")
-    ap.add_argument("--decoder-arch", choices=["likosun", "govuvik"], default="likosun",
-                    help="with --decoder-lm: which design to time (govuvik: window attention beside gated linear attention, mLSTM, routed experts)")
+    ap.add_argument("--decoder-arch", choices=["likosun", "govuvik", "namalix"], default="likosun",
+                    help="with --decoder-lm: which design to time (govuvik: window attention beside gated linear attention, mLSTM, routed experts; "
+                         "namalix: sigmoid attention, retention, delta rule, clamped routed experts)")
     ap.add_argument("--decoder-sizes", default="w2048,w4096", help="comma-separated names out of " + ",".join(DECODER_SIZES))
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--decode-batch", type=int, default=32)
     ap.add_argument("--context", type=int, default=2048)
     args = ap.parse_args()
     if args.decoder_lm:
-        govuvik_arm(args) if args.decoder_arch == "govuvik" else decoder_lm_arm(args)
+        {"govuvik": govuvik_arm, "namalix": namalix_arm}.get(args.decoder_arch, decoder_lm_arm)(args)
         return
     if args.impl == "reference":
         reference_arm(args)
