@@ -1029,8 +1029,9 @@ int finalize_parallel_layer(b200_dlm* h, int i, std::vector<void*>& drop) {
     if (!h->f32 && a.dim % 16 == 0 && a.vdim % 16 == 0) {     // bf16 cache, fragment-sized heads: the tensor-core kernel, if it fits
       const size_t Hh = H, QS = L.Nq + 8, KS = L.Nk + 8, VS = L.Nv + 8;
       const size_t sm = 2 * (16 * QS + 32 * KS + 32 * VS + Hh * 16 * 40) + 4 * (Hh * 16 * 40 + Hh * std::max<size_t>(Hh, 16) + Hh);
-      const int items = ceil_div(H * ceil_div(a.vdim, 64), 8);
-      if (sm <= 220 * 1024 && items <= 4) { L.sig_mma = add_sig(h, H, 16 * H); L.mma_items = items <= 2 ? items : 4; L.mma_smem = sm; }
+      const int items16 = ceil_div(H * ceil_div(a.vdim, 64), 16), items8 = ceil_div(H * ceil_div(a.vdim, 64), 8);
+      // 16 warps when that leaves a warp at most two accumulator items (128 registers per thread), else 8 warps with up to four
+      if (sm <= 220 * 1024 && items8 <= 4) { L.sig_mma = add_sig(h, H, 16 * H); L.mma_items = items16 <= 2 ? -items16 : (items8 <= 2 ? items8 : 4); L.mma_smem = sm; }
     }
   } else if (ret) {
     B200_TRY(h->weights.alloc_t(&L.head_decay, (size_t)H, false));
@@ -1097,9 +1098,9 @@ int sigmoid_attention(b200_dlm* h, const Layer& L, int n_tok, int max_ctx) {
   static bool attr_set = false;
   if (!attr_set) {
     B200_CUDA(cudaFuncSetAttribute(sigmoid_attn_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    B200_CUDA(cudaFuncSetAttribute(sigmoid_attn_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-    B200_CUDA(cudaFuncSetAttribute(sigmoid_attn_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-    B200_CUDA(cudaFuncSetAttribute(sigmoid_attn_mma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+    B200_CUDA(cudaFuncSetAttribute((sigmoid_attn_mma_kernel<1, 16>), cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+    B200_CUDA(cudaFuncSetAttribute((sigmoid_attn_mma_kernel<2, 16>), cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+    B200_CUDA(cudaFuncSetAttribute((sigmoid_attn_mma_kernel<4, 8>), cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
     attr_set = true;
   }
   SigmoidAttnParams p;
@@ -1122,9 +1123,9 @@ int sigmoid_attention(b200_dlm* h, const Layer& L, int n_tok, int max_ctx) {
   if (mma) {
     if constexpr (sizeof(T) == 2) {
       const dim3 grid(s.count, nsplit);
-      if (L.mma_items == 1) B200_LAUNCH(sigmoid_attn_mma_kernel<1>, grid, 256, L.mma_smem, h->stream, p);
-      else if (L.mma_items == 2) B200_LAUNCH(sigmoid_attn_mma_kernel<2>, grid, 256, L.mma_smem, h->stream, p);
-      else B200_LAUNCH(sigmoid_attn_mma_kernel<4>, grid, 256, L.mma_smem, h->stream, p);
+      if (L.mma_items == -1) B200_LAUNCH((sigmoid_attn_mma_kernel<1, 16>), grid, 512, L.mma_smem, h->stream, p);
+      else if (L.mma_items == -2) B200_LAUNCH((sigmoid_attn_mma_kernel<2, 16>), grid, 512, L.mma_smem, h->stream, p);
+      else B200_LAUNCH((sigmoid_attn_mma_kernel<4, 8>), grid, 256, L.mma_smem, h->stream, p);
     }
   } else {
     B200_LAUNCH(sigmoid_attn_kernel<T>, dim3(s.count, nsplit), 256, one ? L.smem_one : L.attn_smem, h->stream, p);

@@ -289,11 +289,20 @@ __global__ void __launch_bounds__(128) sigmoid_attn_merge_kernel(const float* __
 // request with all H heads, a key tile 32 keys.  Per key tile: (1) scores Q_g K^T per head as mma.sync m16n8k16 (queries rounded
 // to bf16 once, fp32 accumulate), cap, bias and sigmoid in fp32 on the accumulator registers, weights into shared memory as
 // fp32; (2) the mix over heads in fp32, one warp per token, lane = key, the mixed weights going back as bf16; (3) O_h += W'_h V
-// on the tensor cores, the accumulators of a warp's NI items (head, 64 value columns) in registers.
+// on the tensor cores, the accumulators of a warp's NI items (head, 64 value columns) in registers.  16 warps per CTA when that
+// leaves a warp at most two items, else 8.
 // ---------------------------------------------------------------------------------------------------------------------------
-template <int NI>
-__global__ void __launch_bounds__(256) sigmoid_attn_mma_kernel(SigmoidAttnParams p) {
-  constexpr int QT = 16, KT = 32, SS = 40, PS = 40;
+// the same weight with the hardware exponential and reciprocal (2 ulp each: far below the bf16 rounding of the operands around it)
+__device__ __forceinline__ float sigmoid_weight_fast(float s, float softcap, float inv_cap, float bias) {
+  if (softcap > 0.f) s = softcap * (1.f - __fdividef(2.f, 1.f + __expf(2.f * s * inv_cap)));      // tanh(z) = 1 - 2 / (1 + e^2z)
+  return __fdividef(1.f, 1.f + __expf(-(s + bias)));
+}
+
+// Keys of a tile are copied asynchronously while the previous tile's mix and weighted sums run, values while the tile's own
+// scores and mix run: K and V have one buffer each and no thread waits for a load it has just issued.
+template <int NI, int NW>      // accumulator items per warp, warps per CTA
+__global__ void __launch_bounds__(NW * 32) sigmoid_attn_mma_kernel(SigmoidAttnParams p) {
+  constexpr int QT = 16, KT = 32, SS = 40, PS = 40, NT = NW * 32;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int H = p.H, G = p.G, dim = p.dim, vdim = p.vdim, rep = H / G;
   const int Nq = H * dim, Nk = G * dim, Nv = G * vdim, QS = Nq + 8, KS = Nk + 8, VS = Nv + 8, VC = (vdim + 63) / 64;
@@ -314,19 +323,40 @@ __global__ void __launch_bounds__(256) sigmoid_attn_mma_kernel(SigmoidAttnParams
   const int n_kt = kmax / KT + 1;
   const int per = (n_kt + p.nsplit - 1) / p.nsplit;
   const int kt0 = split * per, kt1 = min(n_kt, kt0 + per);
+  const float inv_cap = p.softcap > 0.f ? 1.f / p.softcap : 0.f;
+  const int kw = Nk / 8, vw = Nv / 8;
+  // rows past the last key are zero-filled (their weights are zero, they must be finite)
+  auto load_keys = [&](int kt) {
+    const int kb = kt * KT, nk = min(KT, kmax + 1 - kb);
+    const bf16* src = kc + (long long)kb * Nk;
+    for (int i = threadIdx.x; i < KT * kw; i += NT) {
+      const int j = i / kw, e = i - j * kw;
+      cp_async_16_or_zero(Ks + j * KS + e * 8, j < nk ? src + (long long)j * Nk + e * 8 : kc, j < nk);
+    }
+  };
+  auto load_values = [&](int kt) {
+    const int kb = kt * KT, nk = min(KT, kmax + 1 - kb);
+    const bf16* src = vc + (long long)kb * Nv;
+    for (int i = threadIdx.x; i < KT * vw; i += NT) {
+      const int j = i / vw, e = i - j * vw;
+      cp_async_16_or_zero(Vs + j * VS + e * 8, j < nk ? src + (long long)j * Nv + e * 8 : vc, j < nk);
+    }
+  };
+  if (kt0 < kt1) load_keys(kt0);
+  asm volatile("cp.async.commit_group;" ::: "memory");
 
-  for (int i = threadIdx.x; i < QT * (Nq / 2); i += 256) {
+  for (int i = threadIdx.x; i < QT * (Nq / 2); i += NT) {
     const int qt = i / (Nq / 2), e = (i - qt * (Nq / 2)) * 2;
     float2 v = make_float2(0.f, 0.f);
     if (qt < nt) v = *reinterpret_cast<const float2*>(p.q + (long long)(tok0 + qt) * p.ldq + e);
     *reinterpret_cast<unsigned*>(Qs + qt * QS + e) = pack_bf16(v.x, v.y);
   }
   if (H <= 16) {      // rows padded to 16 entries (zeros) for the register-blocked mix
-    for (int i = threadIdx.x; i < H * 16; i += 256) mixs[i] = (i & 15) < H ? p.mix[(i >> 4) * H + (i & 15)] : 0.f;
+    for (int i = threadIdx.x; i < H * 16; i += NT) mixs[i] = (i & 15) < H ? p.mix[(i >> 4) * H + (i & 15)] : 0.f;
   } else {
-    for (int i = threadIdx.x; i < H * H; i += 256) mixs[i] = p.mix[i];
+    for (int i = threadIdx.x; i < H * H; i += NT) mixs[i] = p.mix[i];
   }
-  for (int i = threadIdx.x; i < H; i += 256) bs[i] = p.bias[i];
+  for (int i = threadIdx.x; i < H; i += NT) bs[i] = p.bias[i];
   float oacc[NI][8][4];
 #pragma unroll
   for (int a = 0; a < NI; ++a)
@@ -336,25 +366,13 @@ __global__ void __launch_bounds__(256) sigmoid_attn_mma_kernel(SigmoidAttnParams
   for (int kt = kt0; kt < kt1; ++kt) {
     const int kb = kt * KT;
     const int nk = min(KT, kmax + 1 - kb);
-    __syncthreads();
-    {   // keys and values of the tile: 16-byte loads; rows past the last key are zero (their weights are zero, they must be finite)
-      const int kw = Nk / 8, vw = Nv / 8;
-      const uint4* k4 = reinterpret_cast<const uint4*>(kc + (long long)kb * Nk);
-      const uint4* v4 = reinterpret_cast<const uint4*>(vc + (long long)kb * Nv);
-#pragma unroll 4
-      for (int i = threadIdx.x; i < KT * kw; i += 256) {
-        const int j = i / kw, e = i - j * kw;
-        *reinterpret_cast<uint4*>(Ks + j * KS + e * 8) = j < nk ? k4[i] : make_uint4(0u, 0u, 0u, 0u);
-      }
-#pragma unroll 4
-      for (int i = threadIdx.x; i < KT * vw; i += 256) {
-        const int j = i / vw, e = i - j * vw;
-        *reinterpret_cast<uint4*>(Vs + j * VS + e * 8) = j < nk ? v4[i] : make_uint4(0u, 0u, 0u, 0u);
-      }
-    }
+    __syncthreads();                                              // the previous tile's weighted sums are done with the values
+    load_values(kt);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 1;" ::: "memory");          // this tile's keys (issued a tile ago) have landed
     __syncthreads();
     // (1) scores and weights, one head at a time per warp
-    for (int h = warp; h < H; h += 8) {
+    for (int h = warp; h < H; h += NW) {
       const bf16* qh = Qs + h * dim;
       const bf16* kh = Ks + (h / rep) * dim;
       float sacc[4][4];
@@ -381,16 +399,18 @@ __global__ void __launch_bounds__(256) sigmoid_attn_mma_kernel(SigmoidAttnParams
         for (int e = 0; e < 4; ++e) {
           const int qt = g8 + 8 * (e >> 1), kj = kb + j + (e & 1);
           const bool vis = j + (e & 1) < nk && qt < nt && kj <= p0 + qt;
-          w[e] = vis ? sigmoid_weight(sacc[nb][e], p.softcap, bias) : 0.f;
+          w[e] = vis ? sigmoid_weight_fast(sacc[nb][e], p.softcap, inv_cap, bias) : 0.f;
         }
         *reinterpret_cast<float2*>(dst + g8 * SS + j) = make_float2(w[0], w[1]);
         *reinterpret_cast<float2*>(dst + (g8 + 8) * SS + j) = make_float2(w[2], w[3]);
       }
     }
     __syncthreads();
+    if (kt + 1 < kt1) load_keys(kt + 1);                          // every warp is done with this tile's keys
+    asm volatile("cp.async.commit_group;" ::: "memory");
     // (2) mix over heads; lane = key
     if (H <= 16) {
-      for (int qt = warp; qt < QT; qt += 8) {
+      for (int qt = warp; qt < QT; qt += NW) {
         float raw[16];
 #pragma unroll
         for (int g = 0; g < 16; ++g) raw[g] = g < H ? sw[(g * QT + qt) * SS + lane] : 0.f;
@@ -406,18 +426,19 @@ __global__ void __launch_bounds__(256) sigmoid_attn_mma_kernel(SigmoidAttnParams
         }
       }
     } else {
-      for (int row = warp; row < H * QT; row += 8) {
+      for (int row = warp; row < H * QT; row += NW) {
         const int h = row / QT, qt = row - h * QT;
         float s = 0.f;
         for (int g = 0; g < H; ++g) s = fmaf(mixs[h * H + g], sw[(g * QT + qt) * SS + lane], s);
         pb[row * PS + lane] = __float2bfloat16_rn(s);
       }
     }
+    asm volatile("cp.async.wait_group 1;" ::: "memory");          // this tile's values have landed (the next keys may still fly)
     __syncthreads();
     // (3) weighted sums of the values
 #pragma unroll
     for (int ii = 0; ii < NI; ++ii) {
-      const int it = warp + 8 * ii;
+      const int it = warp + NW * ii;
       if (it >= H * VC) break;
       const int h = it / VC, c0 = (it - h * VC) * 64;
       const bf16* vh = Vs + (h / rep) * vdim + c0;
@@ -437,9 +458,10 @@ __global__ void __launch_bounds__(256) sigmoid_attn_mma_kernel(SigmoidAttnParams
       }
     }
   }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
 #pragma unroll
   for (int ii = 0; ii < NI; ++ii) {
-    const int it = warp + 8 * ii;
+    const int it = warp + NW * ii;
     if (it >= H * VC) break;
     const int h = it / VC, c0 = (it - h * VC) * 64;
 #pragma unroll
