@@ -313,7 +313,8 @@ __global__ void __launch_bounds__(NW * 32) sigmoid_attn_mma_kernel(SigmoidAttnPa
   float* sw = reinterpret_cast<float*>(pb + H * QT * PS);         // [H][16][SS] weights of every head
   float* mixs = sw + H * QT * SS;                                 // [H][max(H, 16)]
   float* bs = mixs + H * max(H, 16);                              // [H]
-  const int tile = blockIdx.x, split = blockIdx.y;
+  // the last tiles of a prompt see the most keys: they are started first, so that the short ones fill the end of the launch
+  const int tile = gridDim.x - 1 - blockIdx.x, split = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g8 = lane >> 2, t4 = lane & 3, mi = lane >> 3;
   const int tok0 = p.tile_row0[tile] / H, nt = p.tile_rows[tile] / H;
   const int p0 = p.tok_pos[tok0];
@@ -357,6 +358,7 @@ __global__ void __launch_bounds__(NW * 32) sigmoid_attn_mma_kernel(SigmoidAttnPa
     for (int i = threadIdx.x; i < H * H; i += NT) mixs[i] = p.mix[i];
   }
   for (int i = threadIdx.x; i < H; i += NT) bs[i] = p.bias[i];
+  for (int i = threadIdx.x; i < H * QT * PS / 2; i += NT) reinterpret_cast<unsigned*>(pb)[i] = 0u;
   float oacc[NI][8][4];
 #pragma unroll
   for (int a = 0; a < NI; ++a)
@@ -410,7 +412,7 @@ __global__ void __launch_bounds__(NW * 32) sigmoid_attn_mma_kernel(SigmoidAttnPa
     asm volatile("cp.async.commit_group;" ::: "memory");
     // (2) mix over heads; lane = key
     if (H <= 16) {
-      for (int qt = warp; qt < QT; qt += NW) {
+      for (int qt = warp; qt < nt; qt += NW) {                    // rows past the tile's tokens stay zero
         float raw[16];
 #pragma unroll
         for (int g = 0; g < 16; ++g) raw[g] = g < H ? sw[(g * QT + qt) * SS + lane] : 0.f;
@@ -428,6 +430,7 @@ __global__ void __launch_bounds__(NW * 32) sigmoid_attn_mma_kernel(SigmoidAttnPa
     } else {
       for (int row = warp; row < H * QT; row += NW) {
         const int h = row / QT, qt = row - h * QT;
+        if (qt >= nt) continue;
         float s = 0.f;
         for (int g = 0; g < H; ++g) s = fmaf(mixs[h * H + g], sw[(g * QT + qt) * SS + lane], s);
         pb[row * PS + lane] = __float2bfloat16_rn(s);
