@@ -434,7 +434,7 @@ int b200_dlm_create(const b200_dlm_config* cfg, b200_dlm** out);
 int b200_dlm_load_tensor(b200_dlm* h, const char* name, const void* data_dev, int dtype, int ndim, const int64_t* shape);
 int b200_dlm_finalize(b200_dlm* h);
 int b200_dlm_destroy(b200_dlm* h);
-/* Allocates what a slot holds per layer (latents [slots][capacity][kv_rank]; or keys and values of `capacity` tokens, the
+/* Allocates what a slot holds per layer (latents [slots][capacity][kv_rank]; or keys and (blended) values of `capacity` tokens, the
  * carried inputs of the causal convolutions and the matrix memories of the recurrent mixers) and the step buffers (up to
  * max_step_tokens new tokens and max_want logit rows per step). */
 int b200_dlm_cache_begin(b200_dlm* h, int slots, int capacity, int max_step_tokens, int max_want, void* stream);
@@ -442,8 +442,8 @@ int b200_dlm_cache_end(b200_dlm* h);
 int b200_dlm_set_stream(b200_dlm* h, void* stream);
 /* "use_tc" (before finalize; 1 = bf16 linears of eligible shapes on the LM's tcgen05 GEMM), "trace_layers" (before cache_begin),
  * "attn_split" (CTAs per attention tile along the keys; 0 = chosen per step), "attn_tc" (0: attention and grouped expert
- * products on the CUDA cores also where a tensor-core kernel would take them; 2: the tensor-core window attention also for
- * single-token requests), "scan_segment" (before cache_begin; tokens per segment of the recurrences: portions of at least two
+ * products on the CUDA cores also where a tensor-core kernel would take them; 2: the tensor-core window / sigmoid attention also for
+ * single-token requests; at 1 the sigmoid attention takes it for single tokens once a request holds 512 keys), "scan_segment" (before cache_begin; tokens per segment of the recurrences: portions of at least two
  * segments run as segments side by side; default 256), "time_kernels" (CUDA events around every
  * operation, summed per class: a step then waits for its own end). */
 int b200_dlm_set_option(b200_dlm* h, const char* name, int value);

@@ -466,3 +466,55 @@ def test_command_line_replays_steps_and_generates(tmp_path, dtype):
             if g != w:
                 assert gap < 1e-3
                 break
+
+
+def random_cfg(seed):
+    """A configuration drawn from the design's whole space: layer order, head counts and sizes, rotation, cap, blending, taps,
+    feed-forward kinds, expert counts; all blending layers share their key/value heads and value size."""
+    import random
+    r = random.Random(seed)
+    width, vocab = r.choice([64, 96, 128, 160, 256, 320]), r.randrange(150, 700)
+    bg, bv = r.choice([1, 2, 4]), r.choice([16, 32, 64])
+    layers = []
+    for i in range(r.randrange(3, 9)):
+        kind = r.choice(["attention", "retention", "delta"]) if i > 2 else ["attention", "retention", "delta"][(i + seed) % 3]
+        mlp = r.choice([None, dense(r.choice([48, 100, 256])), moe(r.choice([2, 4, 8, 12]), 1, r.choice([32, 64])), None])
+        if mlp and mlp["kind"] == "moe":
+            mlp["router"]["top"] = r.randrange(1, min(4, mlp["router"]["experts"]) + 1)
+            mlp["expert"]["limit"], mlp["router"]["scale"] = r.choice([0.5, 1.0, 7.0]), r.choice([1.0, 2.5])
+        if kind == "attention":
+            blend = r.random() < 0.6
+            g = bg if blend else r.choice([1, 2, 4])
+            dim = r.choice([16, 32, 64, 128])
+            rot = r.choice([0, dim // 2, dim])
+            sc = r.choice([None, {"factor": r.choice([2.0, 4.0, 16.0]), "original": r.choice([64, 512, 4096]), "fast": r.choice([8.0, 32.0]), "slow": r.choice([0.5, 1.0, 2.0])}])
+            layers.append(attention(g * r.choice([1, 2, 4]), g, dim, bv if blend else r.choice([16, 32, 48]), r.choice([dim ** -0.5, 0.09, 0.2]), rot_dims=rot,
+                                    base=r.choice([100.0, 10000.0, 500000.0]), scaling=sc if rot else None, softcap=r.choice([0.0, 15.0, 30.0, 50.0]), v_mix=blend, mlp=mlp))
+        elif kind == "retention":
+            hh, dim = r.choice([1, 2, 4, 8]), r.choice([16, 32, 64])
+            layers.append(retention(hh, dim, r.choice([16, 32, 64]), [1.0 - 2.0 ** -r.uniform(3, 10) for _ in range(hh)], rot_dims=r.choice([0, dim // 2, dim]),
+                                    base=r.choice([1000.0, 1000000.0]), mlp=mlp))
+        else:
+            g = r.choice([1, 2, 4])
+            layers.append(delta(g * r.choice([1, 2]), g, r.choice([16, 32, 64, 128]), r.choice([16, 32, 64]), r.choice([2, 3, 4]), mlp=mlp))
+    return make_cfg(layers, vocab=vocab, width=width, emb=width ** 0.5, eps=r.choice([1e-6, 1e-5]))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("seed", range(8))
+def test_random_configurations(seed, dtype):
+    """Whole prompt, prompt + single tokens, and ragged portions of a drawn configuration against the oracle."""
+    cfg = random_cfg(seed)
+    model, orc = build(cfg, dtype, seed=100 + seed)
+    toks = tokens(170, cfg.vocab, 200 + seed)
+    want = orc.forward(toks)
+    with gen_for(model) as gen:
+        assert_close(gen.step([(0, toks)], list(range(len(toks)))), want, dtype, "whole")
+        got = torch.cat([gen.step([(1, toks[:138])], list(range(138)))] + [gen.step([(1, [t])], [0]) for t in toks[138:]])
+        assert_close(got, want, dtype, "prompt, then single tokens")
+        parts, at = [], 0
+        for n in [2, 31, 3, 64, 1, 17, 2, 50]:
+            parts.append(gen.step([(2, toks[at:at + n])], list(range(n))))
+            at += n
+        assert_close(torch.cat(parts), want, dtype, "portions")
+        assert gen.error_flags() == 0
