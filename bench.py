@@ -800,11 +800,11 @@ NAMALIX_SIZES = {
 def _namalix_cfg(size: str):
     from moshi_b200.config import DecoderLMConfig
     W, kinds, H, G, d, Hr, dk, dv, E, top, ff, dff, V = NAMALIX_SIZES[size]
-    moe = {"expert": {"ff": ff, "limit": 7.0}, "kind": "moe", "router": {"experts": E, "scale": 2.5, "top": top}}
+    moe = {"expert": {"ff": ff, "limit": 7.0}, "kind": "moe", "router": {"experts": E, "scale": 2.0, "top": top}}
     mixers = {
-        "attention": {"dim": d, "heads": H, "kv_heads": G, "scale": d ** -0.5, "softcap": 30.0, "v_mix": True, "vdim": d,
+        "attention": {"dim": d, "heads": H, "kv_heads": G, "scale": d ** -0.5, "softcap": 50.0, "v_mix": True, "vdim": d,
                       "rot": {"base": 500000.0, "dims": d // 2, "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}},
-        "retention": {"decay": [1.0 - 2.0 ** (-5 - 5 * i / max(Hr - 1, 1)) for i in range(Hr)], "dim": dk, "heads": Hr, "vdim": dv, "rot": {"base": 1000000.0, "dims": dk}},
+        "retention": {"decay": [1.0 - 2.0 ** (-5 - 5 * i / max(Hr - 1, 1)) for i in range(Hr)], "dim": dk, "heads": Hr, "vdim": dv, "rot": {"base": 100000.0, "dims": dk}},
         "delta": {"conv": 4, "dim": dk, "heads": Hr, "kv_heads": Hr, "vdim": dv},
     }
     layers = [{"type": k, "mixer": mixers[k], "mlp": {"ff": dff, "kind": "dense"} if i == 0 else moe} for i, k in enumerate(kinds)]
