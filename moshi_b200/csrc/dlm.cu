@@ -119,6 +119,9 @@ struct b200_dlm {
   tc::GemmPlanCache plans;
   // parallel-residual block: recurrences that cannot run as segments (the delta rule) take the step's entries whole
   int off_whole_tok0 = 0, off_whole_ntok = 0, off_whole_slot = 0, off_whole_pos0 = 0, off_zero = 0, off_one = 0;
+  int off_chunk_tok0 = 0, off_chunk_nt = 0, off_whole_chunk0 = 0, n_chunks = 0, max_chunks = 0;      // the delta rule's chunks of a step
+  int delta_chunk = 1;                 // option: portions of at least 16 tokens take the chunked delta rule
+  float* gram = nullptr;               // [chunks][heads][DELTA_CH + 2 DELTA_CH^2]
   int vmix_first = -1;                 // the first attention layer that blends values: the later ones blend its values in
   float* small32 = nullptr;            // [tokens][nsmall] fp32 results of the small projection
   void *vfirst = nullptr, *act2 = nullptr;      // T [tokens][G * vdim] values of layer vmix_first; T [tokens * top][2 ff] experts' first product
@@ -1185,6 +1188,44 @@ int routed_experts_glu(b200_dlm* h, const Layer& L, const T* hb, int n_tok) {
   return check_launch("grouped expert products");
 }
 
+template <int R4>
+int launch_delta_chunk(cudaStream_t st, const DeltaChunkParams& p, int n_entries) {
+  constexpr int C = DELTA_CH, DP = 16 * R4;
+  const size_t smem = (size_t)(2 * C * DP + C * 32 + 8 * C * 32 + 2 * C * 32 + C + 2 * C * C) * sizeof(float);
+  static bool attr_set = false;
+  if (!attr_set) {
+    B200_CUDA(cudaFuncSetAttribute(delta_chunk_kernel<R4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attr_set = true;
+  }
+  B200_LAUNCH(delta_chunk_kernel<R4>, dim3(n_entries * p.heads, ceil_div(p.vdim, 32)), 128, smem, st, p);
+  return check_launch("delta_chunk");
+}
+
+// the delta rule of a step's portions in chunks: the chunks' decay sums and the two triangular matrices side by side, then the
+// walk over each request's chunks
+int delta_chunks(b200_dlm* h, const ScanParams& sp) {
+  DeltaChunkParams p;
+  p.prep = sp.prep; p.vprep = sp.vprep; p.gates = sp.tokM; p.prow = sp.prow; p.gram = h->gram;
+  p.chunk_tok0 = h->meta_dev + h->off_chunk_tok0; p.chunk_nt = h->meta_dev + h->off_chunk_nt; p.ent_chunk0 = h->meta_dev + h->off_whole_chunk0;
+  p.ent_tok0 = h->meta_dev + h->off_whole_tok0; p.ent_ntok = h->meta_dev + h->off_whole_ntok; p.ent_slot = h->meta_dev + h->off_whole_slot;
+  p.ent_pos0 = h->meta_dev + h->off_whole_pos0;
+  p.St = sp.St; p.out = sp.out; p.heads = sp.heads; p.dim = sp.dim; p.vdim = sp.vdim;
+  const size_t gsm = (size_t)(2 * DELTA_CH * (sp.dim + 1) + 2 * DELTA_CH) * sizeof(float);
+  static bool attr_set = false;
+  if (!attr_set) {
+    B200_CUDA(cudaFuncSetAttribute(delta_gram_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((2 * DELTA_CH * 257 + 2 * DELTA_CH) * sizeof(float))));
+    attr_set = true;
+  }
+  B200_LAUNCH(delta_gram_kernel, dim3(h->n_chunks, sp.heads), 256, gsm, h->stream, p);
+  B200_TRY(check_launch("delta_gram"));
+  const int d = sp.dim;
+  if (d <= 16) return launch_delta_chunk<1>(h->stream, p, h->n_entries);
+  if (d <= 32) return launch_delta_chunk<2>(h->stream, p, h->n_entries);
+  if (d <= 64) return launch_delta_chunk<4>(h->stream, p, h->n_entries);
+  if (d <= 128) return launch_delta_chunk<8>(h->stream, p, h->n_entries);
+  return launch_delta_chunk<16>(h->stream, p, h->n_entries);
+}
+
 template <typename T>
 int step_parallel(b200_dlm* h, int n_tok, int n_want, int max_ctx, float* logits_out) {
   const b200_dlm_config& c = h->cfg;
@@ -1232,9 +1273,11 @@ int step_parallel(b200_dlm* h, int n_tok, int n_want, int max_ctx, float* logits
               if (a.conv_taps > 1) B200_LAUNCH(conv_carry_kernel<T>, n_tok, 256, 0, st, proj, (long long)L.ldp, L.qkv_hist, C, a.conv_taps - 1, tok_slot, tok_pos, tok_last));
         sp.qscale = 1.f / sqrtf((float)a.dim); sp.z = h->small32 + L.s_ba;
         const ScanLayout lay = scan_layout<MODE_DELTA>(h, sp, true);
+        const bool chunked = h->delta_chunk && h->max_entry_tokens >= 16 && h->gram != nullptr;      // prompts: chunks of tokens at once; single tokens: the scan
+        if (chunked) { sp.lpc = 0; sp.rows = 0; sp.prow = (2 * a.dim + 2 + 3) / 4 * 4; }            // plain rows
         TIMED(CLS_RECURRENT, B200_LAUNCH(delta_prep_kernel, n_tok, 256, (size_t)2 * a.kv_heads * sizeof(float), st, sp, h->qkv32, a.kv_heads, L.A_log, L.dt_bias, (long long)L.nsmall);
               B200_TRY(check_launch("delta_prep"));
-              B200_TRY(scan_run<MODE_DELTA>(h, sp, lay, true)));
+              if (chunked) B200_TRY(delta_chunks(h, sp)); else B200_TRY(scan_run<MODE_DELTA>(h, sp, lay, true)));
         TIMED(CLS_ELEMENTWISE, B200_LAUNCH(head_norm_gate_kernel<T>, (unsigned)ceil_div64(rows, 4), 128, 0, st, h->scan32, L.rnorm, 0, proj, (long long)L.ldp, L.p_g, 1, ob,
                                            a.heads, a.vdim, rows, c.norm_eps));
       }
@@ -1370,6 +1413,8 @@ int b200_dlm_set_option(b200_dlm* h, const char* name, int value) {
     h->time_kernels = value != 0;
   } else if (n == "scan_segment") {
     h->scan_seg = value < 8 ? 8 : value;
+  } else if (n == "delta_chunk") {
+    h->delta_chunk = value != 0;
   } else if (n == "attn_split") {
     h->attn_split = value < 0 ? 0 : value;
   } else {
@@ -1594,6 +1639,10 @@ int b200_dlm_cache_begin(b200_dlm* h, int slots, int capacity, int max_step_toke
     B200_TRY(A.alloc_t(&h->segM, nseg * max_heads * 4));
     B200_TRY(A.alloc_t(&h->tokM, T * max_heads * 4));
     h->max_seg_units = (int)nseg;
+    h->max_chunks = max_step_tokens / DELTA_CH + std::min(slots, max_step_tokens) + 1;
+    bool any_delta = false;
+    for (auto& L : h->layers) any_delta |= L.c.mixer == B200_MIXER_DELTA;
+    if (any_delta) B200_TRY(A.alloc_t(&h->gram, (size_t)h->max_chunks * max_heads * (DELTA_CH + 2 * DELTA_CH * DELTA_CH)));
     B200_TRY(A.alloc_t(&h->gate32, T * max_gate));
     B200_TRY(A.alloc(&h->ffo, T * W * es));
     B200_TRY(A.alloc(&h->vfirst, T * max_nv * es));
@@ -1689,6 +1738,9 @@ int b200_dlm_cache_begin(b200_dlm* h, int slots, int capacity, int max_step_toke
   h->off_whole_pos0 = off; off += max_entries;
   h->off_zero = off; off += max_entries;
   h->off_one = off; off += max_entries;
+  h->off_whole_chunk0 = off; off += max_entries;
+  h->off_chunk_tok0 = off; off += std::max(h->max_chunks, 1);
+  h->off_chunk_nt = off; off += std::max(h->max_chunks, 1);
   for (auto& s : h->sigs) {
     max_tiles = (size_t)ceil_div64((int64_t)max_step_tokens * s.H, s.rpt) + (size_t)std::min(slots, max_step_tokens);
     s.off_row0 = off; off += (int)max_tiles;
@@ -1742,7 +1794,7 @@ int b200_dlm_step(b200_dlm* h, int n_entries, const int32_t* slots_host, const i
   // the previous step's metadata copy must have left the pinned block
   B200_CUDA(cudaEventSynchronize(h->ev_meta));
   int* m = h->meta_pin;
-  int t = 0, max_ctx = 0, n_seg_units = 0;
+  int t = 0, max_ctx = 0, n_seg_units = 0, n_chunks = 0;
   h->units.clear();
   for (auto& s : h->sigs) s.count = 0;
   for (int e = 0; e < n_entries; ++e) {
@@ -1770,6 +1822,10 @@ int b200_dlm_step(b200_dlm* h, int n_entries, const int32_t* slots_host, const i
     }
     m[h->off_whole_tok0 + e] = t; m[h->off_whole_ntok + e] = n; m[h->off_whole_slot + e] = s; m[h->off_whole_pos0 + e] = base;
     m[h->off_zero + e] = 0; m[h->off_one + e] = 1;
+    if (h->max_chunks) {
+      m[h->off_whole_chunk0 + e] = n_chunks;
+      for (int c0 = 0; c0 < n; c0 += DELTA_CH, ++n_chunks) { m[h->off_chunk_tok0 + n_chunks] = t + c0; m[h->off_chunk_nt + n_chunks] = std::min(DELTA_CH, n - c0); }
+    }
     const int first = t, lastt = t + n - 1;
     for (int i = 0; i < n; ++i, ++t) {
       m[h->off_tok + t] = tokens_host[t];
@@ -1785,6 +1841,7 @@ int b200_dlm_step(b200_dlm* h, int n_entries, const int32_t* slots_host, const i
   B200_CUDA(cudaEventRecord(h->ev_meta, h->stream));
   h->n_entries = n_entries;
   h->n_units = (int)h->units.size();
+  h->n_chunks = n_chunks;
   h->max_entry_tokens = 0;
   for (int e = 0; e < n_entries; ++e) h->max_entry_tokens = std::max(h->max_entry_tokens, (int)counts_host[e]);
   int rc;

@@ -525,10 +525,191 @@ __global__ void __launch_bounds__(256) delta_prep_kernel(ScanParams p, const flo
   }
   for (int h = threadIdx.x; h < heads; h += 256) {
     const float* z = p.z + t * ldz;
-    dst[h * p.prow + 2 * Dp] = expf(-expf(A_log[h]) * softplusf(z[heads + h] + dt_bias[h]));
-    dst[h * p.prow + 2 * Dp + 1] = sigmoidf(z[h]);
+    const float lg = -expf(A_log[h]) * softplusf(z[heads + h] + dt_bias[h]), be = sigmoidf(z[h]);
+    dst[h * p.prow + 2 * Dp] = expf(lg);
+    dst[h * p.prow + 2 * Dp + 1] = be;
+    if (p.tokM) { p.tokM[(t * heads + h) * 4] = lg; p.tokM[(t * heads + h) * 4 + 1] = be; }      // the chunked form reads the logarithm
   }
   for (int i = threadIdx.x; i < heads * vdim; i += 256) p.vprep[t * heads * vdim + i] = siluf(c[2 * G * dim + i]);
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// The gated delta rule over a portion, in chunks of DELTA_CH tokens (prompts; single tokens keep matrix_memory_scan_kernel).
+// With S_0 the state in front of a chunk, L_t the sum of log g over the chunk's tokens up to t, and u_t what token t writes:
+//   S_t = e^(L_t) S_0 + sum_{i <= t} e^(L_t - L_i) k_i u_i^T
+//   u_t + sum_{i < t} A[t][i] u_i = beta_t (v_t - e^(L_t) S_0^T k_t),        A[t][i] = beta_t e^(L_t - L_i) (k_t . k_i)
+//   o_t = e^(L_t) S_0^T q_t + sum_{i <= t} P[t][i] u_i,                       P[t][i] = e^(L_t - L_i) (k_i . q_t)
+// so a chunk costs three products against the state (K S_0, Q S_0 and the state's update) that run over all tokens at once, and
+// one forward substitution over the chunk's tokens (unit lower-triangular, the same sums the token-by-token form makes).  Every
+// exponent is <= 0: no decay is ever inverted.  delta_gram_kernel computes L, A and P for every (chunk, head) side by side;
+// delta_chunk_kernel walks a request's chunks in order.
+// ---------------------------------------------------------------------------------------------------------------------------
+constexpr int DELTA_CH = 32;
+
+struct DeltaChunkParams {
+  const float* prep;        // [tokens][heads][prow]: q (scaled) | k, plain rows of `dim` each
+  const float* vprep;       // [tokens][heads * vdim]
+  const float* gates;       // [tokens][heads][4]: log g, beta
+  int prow;
+  float* gram;              // [chunks][heads][DELTA_CH + 2 * DELTA_CH * DELTA_CH]: L | A | P
+  const int* chunk_tok0;    // per chunk: first token of the step, tokens
+  const int* chunk_nt;
+  const int* ent_chunk0;    // per entry: its first chunk
+  const int* ent_tok0; const int* ent_ntok; const int* ent_slot; const int* ent_pos0;
+  float* St;                // [slots][heads][vdim][dim]
+  float* out;               // [tokens][heads * vdim]
+  int heads, dim, vdim;
+};
+
+__global__ void __launch_bounds__(256) delta_gram_kernel(DeltaChunkParams p) {
+  constexpr int C = DELTA_CH;
+  extern __shared__ float gsm[];
+  const int ck = blockIdx.x, head = blockIdx.y, dim = p.dim, DS = dim + 1;
+  float* ks = gsm;                     // [C][DS]
+  float* qs = ks + C * DS;             // [C][DS]
+  float* L = qs + C * DS;              // [C]
+  float* be = L + C;                   // [C]
+  const int tok0 = p.chunk_tok0[ck], nt = p.chunk_nt[ck];
+  for (int i = threadIdx.x; i < C * dim; i += 256) {
+    const int t = i / dim, d = i - t * dim;
+    const float* row = p.prep + ((long long)(tok0 + t) * p.heads + head) * p.prow;
+    qs[t * DS + d] = t < nt ? row[d] : 0.f;
+    ks[t * DS + d] = t < nt ? row[dim + d] : 0.f;
+  }
+  if (threadIdx.x == 0) {
+    float acc = 0.f;
+    for (int t = 0; t < C; ++t) {
+      if (t < nt) acc += p.gates[((long long)(tok0 + t) * p.heads + head) * 4];
+      L[t] = acc;
+      be[t] = t < nt ? p.gates[((long long)(tok0 + t) * p.heads + head) * 4 + 1] : 0.f;
+    }
+  }
+  __syncthreads();
+  float* g = p.gram + ((long long)ck * p.heads + head) * (C + 2 * C * C);
+  if (threadIdx.x < C) g[threadIdx.x] = L[threadIdx.x];
+  for (int i = threadIdx.x; i < C * C; i += 256) {
+    const int t = i / C, j = i - t * C;
+    float a = 0.f, pq = 0.f;
+    if (j <= t && t < nt) {
+      float kk = 0.f, kq = 0.f;
+      for (int d = 0; d < dim; ++d) { kk = fmaf(ks[t * DS + d], ks[j * DS + d], kk); kq = fmaf(ks[j * DS + d], qs[t * DS + d], kq); }
+      const float dec = expf(L[t] - L[j]);
+      pq = dec * kq;
+      if (j < t) a = be[t] * dec * kk;
+    }
+    g[C + i] = a;
+    g[C + C * C + i] = pq;
+  }
+}
+
+// A CTA owns 32 columns of one (request, head): lane = column, warp w owns rows [w * 4 R4, (w + 1) * 4 R4) of the state in
+// registers.  Grid: (entries * heads, ceil(vdim / 32)).
+template <int R4>      // float4 groups of rows per thread: dim <= 16 R4
+__global__ void __launch_bounds__(128) delta_chunk_kernel(DeltaChunkParams p) {
+  constexpr int C = DELTA_CH, R = 4 * R4, DP = 4 * R;        // rows per thread, padded key size
+  extern __shared__ __align__(16) float csm[];
+  float* ks = csm;                     // [C][DP]
+  float* qs = ks + C * DP;             // [C][DP]
+  float* vs = qs + C * DP;             // [C][32]
+  float* wp = vs + C * 32;             // [4][C][32] partial K S_0
+  float* op = wp + 4 * C * 32;         // [4][C][32] partial Q S_0, then [0]: e^(L_t) Q S_0
+  float* us = op + 4 * C * 32;         // [C][32] what the tokens write
+  float* uw = us + C * 32;             // [C][32] the same, decayed to the chunk's end
+  float* gm = uw + C * 32;             // [C + 2 C C]: L | A | P
+  const int heads = p.heads, dim = p.dim, vdim = p.vdim;
+  const int ent = blockIdx.x / heads, head = blockIdx.x - ent * heads;
+  const int tok0 = p.ent_tok0[ent], ntok = p.ent_ntok[ent], slot = p.ent_slot[ent], pos0 = p.ent_pos0[ent], chunk0 = p.ent_chunk0[ent];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, col = blockIdx.y * 32 + lane, row0 = warp * R;
+  const bool live_col = col < vdim;
+  float* Sbase = p.St + ((long long)slot * heads + head) * vdim * dim;
+  float S[R];
+#pragma unroll
+  for (int i = 0; i < R; ++i) S[i] = (pos0 > 0 && live_col && row0 + i < dim) ? Sbase[(long long)col * dim + row0 + i] : 0.f;
+
+  const int n_chunks = (ntok + C - 1) / C;
+  for (int ck = 0; ck < n_chunks; ++ck) {
+    const int t0 = tok0 + ck * C, nt = min(C, ntok - ck * C);
+    __syncthreads();
+    for (int i = threadIdx.x; i < C * DP; i += 128) {
+      const int t = i / DP, d = i - t * DP;
+      const bool ok = t < nt && d < dim;
+      const float* row = p.prep + ((long long)(t0 + t) * heads + head) * p.prow;
+      qs[i] = ok ? row[d] : 0.f;
+      ks[i] = ok ? row[dim + d] : 0.f;
+    }
+    for (int i = threadIdx.x; i < C * 32; i += 128) {
+      const int t = i >> 5, c = blockIdx.y * 32 + (i & 31);
+      vs[i] = (t < nt && c < vdim) ? p.vprep[(long long)(t0 + t) * heads * vdim + head * vdim + c] : 0.f;
+    }
+    {
+      const float* g = p.gram + ((long long)(chunk0 + ck) * heads + head) * (C + 2 * C * C);
+      for (int i = threadIdx.x; i < C + 2 * C * C; i += 128) gm[i] = g[i];
+    }
+    __syncthreads();
+    const float* Lc = gm;
+    const float* A = gm + C;
+    const float* P = gm + C + C * C;
+    // (1) this warp's share of K S_0 and Q S_0 for every token of the chunk
+    for (int t = 0; t < nt; ++t) {
+      float a = 0.f, b = 0.f;
+#pragma unroll
+      for (int j = 0; j < R4; ++j) {
+        const float4 k4 = *reinterpret_cast<const float4*>(ks + t * DP + row0 + 4 * j);
+        const float4 q4 = *reinterpret_cast<const float4*>(qs + t * DP + row0 + 4 * j);
+        a = fmaf(k4.x, S[4 * j], a); a = fmaf(k4.y, S[4 * j + 1], a); a = fmaf(k4.z, S[4 * j + 2], a); a = fmaf(k4.w, S[4 * j + 3], a);
+        b = fmaf(q4.x, S[4 * j], b); b = fmaf(q4.y, S[4 * j + 1], b); b = fmaf(q4.z, S[4 * j + 2], b); b = fmaf(q4.w, S[4 * j + 3], b);
+      }
+      wp[(warp * C + t) * 32 + lane] = a;
+      op[(warp * C + t) * 32 + lane] = b;
+    }
+    __syncthreads();
+    // (2) warp 0: the forward substitution for its column; the other warps: e^(L_t) Q S_0
+    const float Lend = Lc[nt - 1];
+    if (warp == 0) {
+      float u[C];
+#pragma unroll
+      for (int t = 0; t < C; ++t) {
+        float acc = 0.f;
+        if (t < nt) {
+          const float w = (wp[t * 32 + lane] + wp[(C + t) * 32 + lane]) + (wp[(2 * C + t) * 32 + lane] + wp[(3 * C + t) * 32 + lane]);
+          const float beta = p.gates[((long long)(t0 + t) * heads + head) * 4 + 1];
+          acc = beta * (vs[t * 32 + lane] - expf(Lc[t]) * w);
+#pragma unroll
+          for (int i = 0; i < t; ++i) acc = fmaf(-A[t * C + i], u[i], acc);
+        }
+        u[t] = acc;
+        us[t * 32 + lane] = acc;
+        uw[t * 32 + lane] = t < nt ? expf(Lend - Lc[t]) * acc : 0.f;
+      }
+    } else {
+      for (int t = warp - 1; t < nt; t += 3) {
+        const float o = (op[t * 32 + lane] + op[(C + t) * 32 + lane]) + (op[(2 * C + t) * 32 + lane] + op[(3 * C + t) * 32 + lane]);
+        op[t * 32 + lane] = expf(Lc[t]) * o;        // row t of part 0 is read by this thread alone
+      }
+    }
+    __syncthreads();
+    // (3) read-outs (tokens dealt over the warps) and the state at the chunk's end
+    for (int t = warp; t < nt; t += 4) {
+      float o = op[t * 32 + lane];
+      for (int i = 0; i <= t; ++i) o = fmaf(P[t * C + i], us[i * 32 + lane], o);
+      if (live_col) p.out[(long long)(t0 + t) * heads * vdim + head * vdim + col] = o;
+    }
+    const float gall = expf(Lend);
+#pragma unroll
+    for (int i = 0; i < R; ++i) S[i] *= gall;
+    for (int t = 0; t < nt; ++t) {
+      const float w = uw[t * 32 + lane];
+#pragma unroll
+      for (int j = 0; j < R4; ++j) {
+        const float4 k4 = *reinterpret_cast<const float4*>(ks + t * DP + row0 + 4 * j);
+        S[4 * j] = fmaf(k4.x, w, S[4 * j]); S[4 * j + 1] = fmaf(k4.y, w, S[4 * j + 1]); S[4 * j + 2] = fmaf(k4.z, w, S[4 * j + 2]); S[4 * j + 3] = fmaf(k4.w, w, S[4 * j + 3]);
+      }
+    }
+  }
+  if (live_col) {
+#pragma unroll
+    for (int i = 0; i < R; ++i) if (row0 + i < dim) Sbase[(long long)col * dim + row0 + i] = S[i];
+  }
 }
 
 // out = gelu_tanh(gate) * up on the two halves of a concatenated projection

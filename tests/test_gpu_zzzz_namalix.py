@@ -518,3 +518,32 @@ def test_random_configurations(seed, dtype):
             at += n
         assert_close(torch.cat(parts), want, dtype, "portions")
         assert gen.error_flags() == 0
+
+
+@pytest.mark.parametrize("heads,kv,dim,vdim,conv", [(3, 3, 9, 10, 2), (4, 2, 17, 33, 3), (2, 1, 40, 64, 4), (2, 2, 128, 48, 4), (1, 1, 200, 70, 2)])
+def test_delta_rule_in_chunks_equals_token_by_token(heads, kv, dim, vdim, conv):
+    """Portions of at least 16 tokens take the delta rule in chunks of 32 tokens (three products against the state and one forward
+    substitution per chunk); shorter ones and single tokens the token-by-token kernel.  Both against the oracle, for every
+    register layout of the chunk kernel (key sizes up to 16, 32, 64, 128, 256), with chunks that end ragged, portions that start
+    on a carried state, a mixed batch, and decays near one so that the state carries across many chunks."""
+    cfg = make_cfg([delta(heads, kv, dim, vdim, conv, mlp=dense(24))], vocab=80, width=48)
+    model, orc = build(cfg, torch.float32, seed=41, edit=keep_long)
+    reqs = [tokens(150, cfg.vocab, 91), tokens(20, cfg.vocab, 92), tokens(77, cfg.vocab, 93)]
+    want = [orc.forward(r) for r in reqs]
+    with gen_for(model) as gen:
+        for chunked in (1, 0):
+            gen.set_option("delta_chunk", chunked)
+            for s in range(3):
+                gen.release(s)
+            assert_close(gen.step([(0, reqs[0])], list(range(150))), want[0], torch.float32, f"one portion (chunks {chunked})")
+            gen.release(0)
+            parts = [gen.step([(0, reqs[0][:70])], list(range(70))), gen.step([(0, reqs[0][70:73])], [0, 1, 2]), gen.step([(0, reqs[0][73:110])], list(range(37)))]
+            parts += [gen.step([(0, [t])], [0]) for t in reqs[0][110:]]
+            assert_close(torch.cat(parts), want[0], torch.float32, f"70 + 3 + 37 tokens, then one by one (chunks {chunked})")
+            gen.release(0)
+            gen.step([(2, reqs[0][:40]), (0, reqs[2][:33])])
+            got = gen.step([(2, reqs[0][40:]), (1, reqs[1]), (0, reqs[2][33:34])], list(range(110 + 20 + 1)))
+            assert_close(got[:110], want[0][40:], torch.float32, f"110 tokens on a history of 40 (chunks {chunked})")
+            assert_close(got[110:130], want[1], torch.float32, f"a fresh request of 20 beside them (chunks {chunked})")
+            assert_close(got[130:], want[2][33:34], torch.float32, f"a single token beside them (chunks {chunked})")
+        assert gen.error_flags() == 0
