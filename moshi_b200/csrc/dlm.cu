@@ -121,7 +121,7 @@ struct b200_dlm {
   int off_whole_tok0 = 0, off_whole_ntok = 0, off_whole_slot = 0, off_whole_pos0 = 0, off_zero = 0, off_one = 0;
   int off_chunk_tok0 = 0, off_chunk_nt = 0, off_whole_chunk0 = 0, n_chunks = 0, max_chunks = 0;      // the delta rule's chunks of a step
   int delta_chunk = 1;                 // option: portions of at least 16 tokens take the chunked delta rule
-  float* gram = nullptr;               // [chunks][heads][DELTA_CH + 2 DELTA_CH^2]
+  float* gram = nullptr;               // [chunks][heads][2 DELTA_CH + 2 DELTA_CH^2]
   int vmix_first = -1;                 // the first attention layer that blends values: the later ones blend its values in
   float* small32 = nullptr;            // [tokens][nsmall] fp32 results of the small projection
   void *vfirst = nullptr, *act2 = nullptr;      // T [tokens][G * vdim] values of layer vmix_first; T [tokens * top][2 ff] experts' first product
@@ -1190,14 +1190,14 @@ int routed_experts_glu(b200_dlm* h, const Layer& L, const T* hb, int n_tok) {
 
 template <int R4>
 int launch_delta_chunk(cudaStream_t st, const DeltaChunkParams& p, int n_entries) {
-  constexpr int C = DELTA_CH, DP = 16 * R4;
-  const size_t smem = (size_t)(2 * C * DP + C * 32 + 8 * C * 32 + 2 * C * 32 + C + 2 * C * C) * sizeof(float);
+  constexpr int C = DELTA_CH, DP = 32 * R4;
+  const size_t smem = (size_t)((R4 <= 4 ? 2 : 1) * (2 * C * DP + C * 32 + 2 * C + 2 * C * C) + 16 * C * 32 + 3 * C * 32 + 2 * C) * sizeof(float);
   static bool attr_set = false;
   if (!attr_set) {
     B200_CUDA(cudaFuncSetAttribute(delta_chunk_kernel<R4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     attr_set = true;
   }
-  B200_LAUNCH(delta_chunk_kernel<R4>, dim3(n_entries * p.heads, ceil_div(p.vdim, 32)), 128, smem, st, p);
+  B200_LAUNCH(delta_chunk_kernel<R4>, dim3(n_entries * p.heads, ceil_div(p.vdim, 32)), 256, smem, st, p);
   return check_launch("delta_chunk");
 }
 
@@ -1210,20 +1210,19 @@ int delta_chunks(b200_dlm* h, const ScanParams& sp) {
   p.ent_tok0 = h->meta_dev + h->off_whole_tok0; p.ent_ntok = h->meta_dev + h->off_whole_ntok; p.ent_slot = h->meta_dev + h->off_whole_slot;
   p.ent_pos0 = h->meta_dev + h->off_whole_pos0;
   p.St = sp.St; p.out = sp.out; p.heads = sp.heads; p.dim = sp.dim; p.vdim = sp.vdim;
-  const size_t gsm = (size_t)(2 * DELTA_CH * (sp.dim + 1) + 2 * DELTA_CH) * sizeof(float);
+  const size_t gsm = (size_t)(2 * DELTA_CH * (sp.dim + 1) + 2 * DELTA_CH + DELTA_CH * DELTA_CH) * sizeof(float);
   static bool attr_set = false;
   if (!attr_set) {
-    B200_CUDA(cudaFuncSetAttribute(delta_gram_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((2 * DELTA_CH * 257 + 2 * DELTA_CH) * sizeof(float))));
+    B200_CUDA(cudaFuncSetAttribute(delta_gram_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((2 * DELTA_CH * 257 + 2 * DELTA_CH + DELTA_CH * DELTA_CH) * sizeof(float))));
     attr_set = true;
   }
   B200_LAUNCH(delta_gram_kernel, dim3(h->n_chunks, sp.heads), 256, gsm, h->stream, p);
   B200_TRY(check_launch("delta_gram"));
   const int d = sp.dim;
-  if (d <= 16) return launch_delta_chunk<1>(h->stream, p, h->n_entries);
-  if (d <= 32) return launch_delta_chunk<2>(h->stream, p, h->n_entries);
-  if (d <= 64) return launch_delta_chunk<4>(h->stream, p, h->n_entries);
-  if (d <= 128) return launch_delta_chunk<8>(h->stream, p, h->n_entries);
-  return launch_delta_chunk<16>(h->stream, p, h->n_entries);
+  if (d <= 32) return launch_delta_chunk<1>(h->stream, p, h->n_entries);
+  if (d <= 64) return launch_delta_chunk<2>(h->stream, p, h->n_entries);
+  if (d <= 128) return launch_delta_chunk<4>(h->stream, p, h->n_entries);
+  return launch_delta_chunk<8>(h->stream, p, h->n_entries);
 }
 
 template <typename T>
@@ -1642,7 +1641,7 @@ int b200_dlm_cache_begin(b200_dlm* h, int slots, int capacity, int max_step_toke
     h->max_chunks = max_step_tokens / DELTA_CH + std::min(slots, max_step_tokens) + 1;
     bool any_delta = false;
     for (auto& L : h->layers) any_delta |= L.c.mixer == B200_MIXER_DELTA;
-    if (any_delta) B200_TRY(A.alloc_t(&h->gram, (size_t)h->max_chunks * max_heads * (DELTA_CH + 2 * DELTA_CH * DELTA_CH)));
+    if (any_delta) B200_TRY(A.alloc_t(&h->gram, (size_t)h->max_chunks * max_heads * (2 * DELTA_CH + 2 * DELTA_CH * DELTA_CH)));
     B200_TRY(A.alloc_t(&h->gate32, T * max_gate));
     B200_TRY(A.alloc(&h->ffo, T * W * es));
     B200_TRY(A.alloc(&h->vfirst, T * max_nv * es));

@@ -537,12 +537,13 @@ __global__ void __launch_bounds__(256) delta_prep_kernel(ScanParams p, const flo
 // The gated delta rule over a portion, in chunks of DELTA_CH tokens (prompts; single tokens keep matrix_memory_scan_kernel).
 // With S_0 the state in front of a chunk, L_t the sum of log g over the chunk's tokens up to t, and u_t what token t writes:
 //   S_t = e^(L_t) S_0 + sum_{i <= t} e^(L_t - L_i) k_i u_i^T
-//   u_t + sum_{i < t} A[t][i] u_i = beta_t (v_t - e^(L_t) S_0^T k_t),        A[t][i] = beta_t e^(L_t - L_i) (k_t . k_i)
+//   u_t + sum_{i < t} A[t][i] u_i = b_t,   b_t = beta_t (v_t - e^(L_t) S_0^T k_t),   A[t][i] = beta_t e^(L_t - L_i) (k_t . k_i)
+//   i.e. U = T B with T = (I + A)^-1, unit lower triangular, which depends on the chunk's keys and gates alone
 //   o_t = e^(L_t) S_0^T q_t + sum_{i <= t} P[t][i] u_i,                       P[t][i] = e^(L_t - L_i) (k_i . q_t)
-// so a chunk costs three products against the state (K S_0, Q S_0 and the state's update) that run over all tokens at once, and
-// one forward substitution over the chunk's tokens (unit lower-triangular, the same sums the token-by-token form makes).  Every
-// exponent is <= 0: no decay is ever inverted.  delta_gram_kernel computes L, A and P for every (chunk, head) side by side;
-// delta_chunk_kernel walks a request's chunks in order.
+// so a chunk costs three products against the state (K S_0, Q S_0 and the state's update) and two small triangular products
+// (T B and P U), all of which run over the chunk's tokens at once.  Every exponent is <= 0: no decay is ever inverted.
+// delta_gram_kernel computes L, T and P for every (chunk, head) side by side (the forward substitution that inverts I + A runs
+// there, off the chain); delta_chunk_kernel walks a request's chunks in order.
 // ---------------------------------------------------------------------------------------------------------------------------
 constexpr int DELTA_CH = 32;
 
@@ -551,7 +552,7 @@ struct DeltaChunkParams {
   const float* vprep;       // [tokens][heads * vdim]
   const float* gates;       // [tokens][heads][4]: log g, beta
   int prow;
-  float* gram;              // [chunks][heads][DELTA_CH + 2 * DELTA_CH * DELTA_CH]: L | A | P
+  float* gram;              // [chunks][heads][2 * DELTA_CH + 2 * DELTA_CH * DELTA_CH]: L | beta | T | P
   const int* chunk_tok0;    // per chunk: first token of the step, tokens
   const int* chunk_nt;
   const int* ent_chunk0;    // per entry: its first chunk
@@ -585,8 +586,10 @@ __global__ void __launch_bounds__(256) delta_gram_kernel(DeltaChunkParams p) {
     }
   }
   __syncthreads();
-  float* g = p.gram + ((long long)ck * p.heads + head) * (C + 2 * C * C);
-  if (threadIdx.x < C) g[threadIdx.x] = L[threadIdx.x];
+  float* g = p.gram + ((long long)ck * p.heads + head) * (2 * C + 2 * C * C);
+  if (threadIdx.x < C) { g[threadIdx.x] = L[threadIdx.x]; g[C + threadIdx.x] = be[threadIdx.x]; }
+  g += C;
+  float* As = be + C;                  // [C][C]
   for (int i = threadIdx.x; i < C * C; i += 256) {
     const int t = i / C, j = i - t * C;
     float a = 0.f, pq = 0.f;
@@ -597,25 +600,40 @@ __global__ void __launch_bounds__(256) delta_gram_kernel(DeltaChunkParams p) {
       pq = dec * kq;
       if (j < t) a = be[t] * dec * kk;
     }
-    g[C + i] = a;
+    As[i] = a;
     g[C + C * C + i] = pq;
+  }
+  __syncthreads();
+  // T = (I + A)^-1, unit lower triangular: lane j of warp 0 solves (I + A) x = e_j by forward substitution (x_t = 0 above the diagonal)
+  if (threadIdx.x < C) {
+    const int j = threadIdx.x;
+    float x[C];
+#pragma unroll
+    for (int t = 0; t < C; ++t) {
+      float acc = t == j ? 1.f : 0.f;
+#pragma unroll
+      for (int i = 0; i < t; ++i) acc = fmaf(-As[t * C + i], x[i], acc);
+      x[t] = acc;
+      g[C + t * C + j] = acc;
+    }
   }
 }
 
-// A CTA owns 32 columns of one (request, head): lane = column, warp w owns rows [w * 4 R4, (w + 1) * 4 R4) of the state in
+// A CTA owns 32 columns of one (request, head): lane = column, warp w (of 8) owns rows [w * 4 R4, (w + 1) * 4 R4) of the state in
 // registers.  Grid: (entries * heads, ceil(vdim / 32)).
-template <int R4>      // float4 groups of rows per thread: dim <= 16 R4
-__global__ void __launch_bounds__(128) delta_chunk_kernel(DeltaChunkParams p) {
-  constexpr int C = DELTA_CH, R = 4 * R4, DP = 4 * R;        // rows per thread, padded key size
+template <int R4>      // float4 groups of rows per thread: dim <= 32 R4
+__global__ void __launch_bounds__(256) delta_chunk_kernel(DeltaChunkParams p) {
+  constexpr int C = DELTA_CH, R = 4 * R4, NW = 8, DP = NW * R;        // rows per thread, warps, padded key size
+  constexpr int NBUF = R4 <= 4 ? 2 : 1;                               // what a chunk reads is staged one chunk ahead when two buffers fit
+  constexpr int GM = 2 * C + 2 * C * C, STAGE = 2 * C * DP + C * 32 + GM;
   extern __shared__ __align__(16) float csm[];
-  float* ks = csm;                     // [C][DP]
-  float* qs = ks + C * DP;             // [C][DP]
-  float* vs = qs + C * DP;             // [C][32]
-  float* wp = vs + C * 32;             // [4][C][32] partial K S_0
-  float* op = wp + 4 * C * 32;         // [4][C][32] partial Q S_0, then [0]: e^(L_t) Q S_0
-  float* us = op + 4 * C * 32;         // [C][32] what the tokens write
+  float* wp = csm + NBUF * STAGE;      // [NW][C][32] partial K S_0
+  float* op = wp + NW * C * 32;        // [NW][C][32] partial Q S_0, then [0]: e^(L_t) Q S_0
+  float* us = op + NW * C * 32;        // [C][32] what the tokens write
   float* uw = us + C * 32;             // [C][32] the same, decayed to the chunk's end
-  float* gm = uw + C * 32;             // [C + 2 C C]: L | A | P
+  float* bs = uw + C * 32;             // [C][32] right-hand sides b_t
+  float* eL = bs + C * 32;             // [C] e^(L_t): the decay from the chunk's start to token t
+  float* eW = eL + C;                  // [C] e^(L_end - L_t): from token t to the chunk's end
   const int heads = p.heads, dim = p.dim, vdim = p.vdim;
   const int ent = blockIdx.x / heads, head = blockIdx.x - ent * heads;
   const int tok0 = p.ent_tok0[ent], ntok = p.ent_ntok[ent], slot = p.ent_slot[ent], pos0 = p.ent_pos0[ent], chunk0 = p.ent_chunk0[ent];
@@ -627,76 +645,119 @@ __global__ void __launch_bounds__(128) delta_chunk_kernel(DeltaChunkParams p) {
   for (int i = 0; i < R; ++i) S[i] = (pos0 > 0 && live_col && row0 + i < dim) ? Sbase[(long long)col * dim + row0 + i] : 0.f;
 
   const int n_chunks = (ntok + C - 1) / C;
-  for (int ck = 0; ck < n_chunks; ++ck) {
+  const bool vec = (dim & 3) == 0 && (vdim & 3) == 0;      // rows of q, k and the column slice of v start on 16 bytes
+  // chunk ck into buffer b: q and k rows (zero beyond the chunk's tokens and the key size), the values of this CTA's columns, L | beta | A | P
+  auto stage = [&](int ck, int b) {
+    float* ks = csm + b * STAGE;       // [C][DP]
+    float* qs = ks + C * DP;           // [C][DP]
+    float* vs = qs + C * DP;           // [C][32]
+    float* gm = vs + C * 32;
     const int t0 = tok0 + ck * C, nt = min(C, ntok - ck * C);
-    __syncthreads();
-    for (int i = threadIdx.x; i < C * DP; i += 128) {
-      const int t = i / DP, d = i - t * DP;
-      const bool ok = t < nt && d < dim;
-      const float* row = p.prep + ((long long)(t0 + t) * heads + head) * p.prow;
-      qs[i] = ok ? row[d] : 0.f;
-      ks[i] = ok ? row[dim + d] : 0.f;
+    const float* gl = p.gram + ((long long)(chunk0 + ck) * heads + head) * GM;
+    if (vec) {
+      for (int i = threadIdx.x; i < C * (DP / 4); i += 256) {
+        const int t = i / (DP / 4), d = (i - t * (DP / 4)) * 4;
+        const bool ok = t < nt && d < dim;
+        const float* row = p.prep + ((long long)(t0 + (ok ? t : 0)) * heads + head) * p.prow;
+        cp_async_16_or_zero(qs + t * DP + d, ok ? row + d : row, ok);
+        cp_async_16_or_zero(ks + t * DP + d, ok ? row + dim + d : row, ok);
+      }
+      for (int i = threadIdx.x; i < C * 8; i += 256) {
+        const int t = i >> 3, c = blockIdx.y * 32 + (i & 7) * 4;
+        const bool ok = t < nt && c < vdim;
+        const float* src = p.vprep + (long long)(t0 + (ok ? t : 0)) * heads * vdim + head * vdim + (ok ? c : 0);
+        cp_async_16_or_zero(vs + t * 32 + (i & 7) * 4, src, ok);
+      }
+      for (int i = threadIdx.x; i < GM / 4; i += 256) cp_async_16_or_zero(gm + 4 * i, gl + 4 * i, true);
+    } else {
+      for (int i = threadIdx.x; i < C * DP; i += 256) {
+        const int t = i / DP, d = i - t * DP;
+        const bool ok = t < nt && d < dim;
+        const float* row = p.prep + ((long long)(t0 + (ok ? t : 0)) * heads + head) * p.prow;
+        qs[i] = ok ? row[d] : 0.f;
+        ks[i] = ok ? row[dim + d] : 0.f;
+      }
+      for (int i = threadIdx.x; i < C * 32; i += 256) {
+        const int t = i >> 5, c = blockIdx.y * 32 + (i & 31);
+        vs[i] = (t < nt && c < vdim) ? p.vprep[(long long)(t0 + t) * heads * vdim + head * vdim + c] : 0.f;
+      }
+      for (int i = threadIdx.x; i < GM; i += 256) gm[i] = gl[i];
     }
-    for (int i = threadIdx.x; i < C * 32; i += 128) {
-      const int t = i >> 5, c = blockIdx.y * 32 + (i & 31);
-      vs[i] = (t < nt && c < vdim) ? p.vprep[(long long)(t0 + t) * heads * vdim + head * vdim + c] : 0.f;
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  stage(0, 0);
+  for (int ck = 0; ck < n_chunks; ++ck) {
+    const int t0 = tok0 + ck * C, nt = min(C, ntok - ck * C), buf = NBUF == 2 ? (ck & 1) : 0;
+    const float* ks = csm + buf * STAGE;
+    const float* qs = ks + C * DP;
+    const float* vs = qs + C * DP;
+    const float* gm = vs + C * 32;
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();                   // this chunk has landed for every thread, and every thread is done with the previous one
+    if (NBUF == 2 && ck + 1 < n_chunks) stage(ck + 1, buf ^ 1);
+    if (threadIdx.x < C) {
+      const float lt = gm[threadIdx.x], le = gm[nt - 1];
+      eL[threadIdx.x] = expf(lt);
+      eW[threadIdx.x] = expf(le - lt);
     }
-    {
-      const float* g = p.gram + ((long long)(chunk0 + ck) * heads + head) * (C + 2 * C * C);
-      for (int i = threadIdx.x; i < C + 2 * C * C; i += 128) gm[i] = g[i];
-    }
-    __syncthreads();
-    const float* Lc = gm;
-    const float* A = gm + C;
-    const float* P = gm + C + C * C;
-    // (1) this warp's share of K S_0 and Q S_0 for every token of the chunk
-    for (int t = 0; t < nt; ++t) {
-      float a = 0.f, b = 0.f;
+    const float* Bt = gm + C;
+    const float* A = gm + 2 * C;             // T = (I + A)^-1
+    const float* P = gm + 2 * C + C * C;
+    // (1) this warp's share of K S_0 and Q S_0 for every token of the chunk (rows of tokens past the chunk's end are zero)
+#pragma unroll 2
+    for (int t = 0; t < C; t += 2) {
+      float a0 = 0.f, b0 = 0.f, a1 = 0.f, b1 = 0.f;
 #pragma unroll
       for (int j = 0; j < R4; ++j) {
-        const float4 k4 = *reinterpret_cast<const float4*>(ks + t * DP + row0 + 4 * j);
-        const float4 q4 = *reinterpret_cast<const float4*>(qs + t * DP + row0 + 4 * j);
-        a = fmaf(k4.x, S[4 * j], a); a = fmaf(k4.y, S[4 * j + 1], a); a = fmaf(k4.z, S[4 * j + 2], a); a = fmaf(k4.w, S[4 * j + 3], a);
-        b = fmaf(q4.x, S[4 * j], b); b = fmaf(q4.y, S[4 * j + 1], b); b = fmaf(q4.z, S[4 * j + 2], b); b = fmaf(q4.w, S[4 * j + 3], b);
+        const float4 k0 = *reinterpret_cast<const float4*>(ks + t * DP + row0 + 4 * j), k1 = *reinterpret_cast<const float4*>(ks + (t + 1) * DP + row0 + 4 * j);
+        const float4 q0 = *reinterpret_cast<const float4*>(qs + t * DP + row0 + 4 * j), q1 = *reinterpret_cast<const float4*>(qs + (t + 1) * DP + row0 + 4 * j);
+        a0 = fmaf(k0.x, S[4 * j], a0); a0 = fmaf(k0.y, S[4 * j + 1], a0); a0 = fmaf(k0.z, S[4 * j + 2], a0); a0 = fmaf(k0.w, S[4 * j + 3], a0);
+        b0 = fmaf(q0.x, S[4 * j], b0); b0 = fmaf(q0.y, S[4 * j + 1], b0); b0 = fmaf(q0.z, S[4 * j + 2], b0); b0 = fmaf(q0.w, S[4 * j + 3], b0);
+        a1 = fmaf(k1.x, S[4 * j], a1); a1 = fmaf(k1.y, S[4 * j + 1], a1); a1 = fmaf(k1.z, S[4 * j + 2], a1); a1 = fmaf(k1.w, S[4 * j + 3], a1);
+        b1 = fmaf(q1.x, S[4 * j], b1); b1 = fmaf(q1.y, S[4 * j + 1], b1); b1 = fmaf(q1.z, S[4 * j + 2], b1); b1 = fmaf(q1.w, S[4 * j + 3], b1);
       }
-      wp[(warp * C + t) * 32 + lane] = a;
-      op[(warp * C + t) * 32 + lane] = b;
+      wp[(warp * C + t) * 32 + lane] = a0; wp[(warp * C + t + 1) * 32 + lane] = a1;
+      op[(warp * C + t) * 32 + lane] = b0; op[(warp * C + t + 1) * 32 + lane] = b1;
+      if (t + 2 >= nt) break;
     }
     __syncthreads();
-    // (2) warp 0: the forward substitution for its column; the other warps: e^(L_t) Q S_0
-    const float Lend = Lc[nt - 1];
-    if (warp == 0) {
-      float u[C];
+    // (2) tokens dealt over the warps: b_t and e^(L_t) Q S_0 from the partial sums, then U = T B (four running sums)
+    for (int t = warp; t < nt; t += NW) {
+      float w = 0.f, o = 0.f;
 #pragma unroll
-      for (int t = 0; t < C; ++t) {
-        float acc = 0.f;
-        if (t < nt) {
-          const float w = (wp[t * 32 + lane] + wp[(C + t) * 32 + lane]) + (wp[(2 * C + t) * 32 + lane] + wp[(3 * C + t) * 32 + lane]);
-          const float beta = p.gates[((long long)(t0 + t) * heads + head) * 4 + 1];
-          acc = beta * (vs[t * 32 + lane] - expf(Lc[t]) * w);
-#pragma unroll
-          for (int i = 0; i < t; ++i) acc = fmaf(-A[t * C + i], u[i], acc);
-        }
-        u[t] = acc;
-        us[t * 32 + lane] = acc;
-        uw[t * 32 + lane] = t < nt ? expf(Lend - Lc[t]) * acc : 0.f;
-      }
-    } else {
-      for (int t = warp - 1; t < nt; t += 3) {
-        const float o = (op[t * 32 + lane] + op[(C + t) * 32 + lane]) + (op[(2 * C + t) * 32 + lane] + op[(3 * C + t) * 32 + lane]);
-        op[t * 32 + lane] = expf(Lc[t]) * o;        // row t of part 0 is read by this thread alone
-      }
+      for (int g = 0; g < NW; ++g) { w += wp[(g * C + t) * 32 + lane]; o += op[(g * C + t) * 32 + lane]; }
+      bs[t * 32 + lane] = Bt[t] * (vs[t * 32 + lane] - eL[t] * w);
+      op[t * 32 + lane] = eL[t] * o;          // row t of part 0 is read by this thread alone
     }
     __syncthreads();
-    // (3) read-outs (tokens dealt over the warps) and the state at the chunk's end
-    for (int t = warp; t < nt; t += 4) {
-      float o = op[t * 32 + lane];
-      for (int i = 0; i <= t; ++i) o = fmaf(P[t * C + i], us[i * 32 + lane], o);
-      if (live_col) p.out[(long long)(t0 + t) * heads * vdim + head * vdim + col] = o;
+    for (int t = warp; t < nt; t += NW) {
+      float u0 = bs[t * 32 + lane], u1 = 0.f, u2 = 0.f, u3 = 0.f;
+      int i = 0;
+      for (; i + 4 <= t; i += 4) {
+        u0 = fmaf(A[t * C + i], bs[i * 32 + lane], u0); u1 = fmaf(A[t * C + i + 1], bs[(i + 1) * 32 + lane], u1);
+        u2 = fmaf(A[t * C + i + 2], bs[(i + 2) * 32 + lane], u2); u3 = fmaf(A[t * C + i + 3], bs[(i + 3) * 32 + lane], u3);
+      }
+      for (; i < t; ++i) u0 = fmaf(A[t * C + i], bs[i * 32 + lane], u0);
+      const float u = (u0 + u1) + (u2 + u3);
+      us[t * 32 + lane] = u;
+      uw[t * 32 + lane] = eW[t] * u;
     }
-    const float gall = expf(Lend);
+    __syncthreads();
+    // (3) read-outs (tokens dealt over the warps, four running sums) and the state at the chunk's end
+    for (int t = warp; t < nt; t += NW) {
+      float o0 = op[t * 32 + lane], o1 = 0.f, o2 = 0.f, o3 = 0.f;
+      int i = 0;
+      for (; i + 3 <= t; i += 4) {
+        o0 = fmaf(P[t * C + i], us[i * 32 + lane], o0); o1 = fmaf(P[t * C + i + 1], us[(i + 1) * 32 + lane], o1);
+        o2 = fmaf(P[t * C + i + 2], us[(i + 2) * 32 + lane], o2); o3 = fmaf(P[t * C + i + 3], us[(i + 3) * 32 + lane], o3);
+      }
+      for (; i <= t; ++i) o0 = fmaf(P[t * C + i], us[i * 32 + lane], o0);
+      if (live_col) p.out[(long long)(t0 + t) * heads * vdim + head * vdim + col] = (o0 + o1) + (o2 + o3);
+    }
+    const float gall = expf(gm[nt - 1]);
 #pragma unroll
     for (int i = 0; i < R; ++i) S[i] *= gall;
+#pragma unroll 4
     for (int t = 0; t < nt; ++t) {
       const float w = uw[t * 32 + lane];
 #pragma unroll
@@ -704,6 +765,10 @@ __global__ void __launch_bounds__(128) delta_chunk_kernel(DeltaChunkParams p) {
         const float4 k4 = *reinterpret_cast<const float4*>(ks + t * DP + row0 + 4 * j);
         S[4 * j] = fmaf(k4.x, w, S[4 * j]); S[4 * j + 1] = fmaf(k4.y, w, S[4 * j + 1]); S[4 * j + 2] = fmaf(k4.z, w, S[4 * j + 2]); S[4 * j + 3] = fmaf(k4.w, w, S[4 * j + 3]);
       }
+    }
+    if (NBUF == 1 && ck + 1 < n_chunks) {      // one buffer: the next chunk is staged once every thread has left this one
+      __syncthreads();
+      stage(ck + 1, 0);
     }
   }
   if (live_col) {
