@@ -365,7 +365,8 @@ int b200_frame_read_buffer(b200_frame* f, const char* name, void* dst_dev, int64
  *           B200_MIXER_DELTA: the gated delta rule, S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q, behind causal
  *           convolutions (conv_taps) with silu on q, k, v; q and k are unit vectors per head (q times dim^-1/2) shared by
  *           heads / kv_heads value heads; beta = sigmoid(W_b h), g = exp(-exp(A_log) softplus(W_a h + dt_bias)); the result is
- *           RMS-normed per head with one weight row and gated by silu(W_g h)
+ *           RMS-normed per head with one weight row and gated by silu(W_g h); prompts run in chunks of 32 tokens (three products
+ *           against the state and two triangular ones per chunk), single tokens one by one
  *   mlp     B200_MLP_DENSE_GATED_GELU: W_down (gelu_tanh(W_gate h) * (W_up h))
  *           B200_MLP_MOE_CLAMPED_GLU: routed experts W_down (g * sigmoid(1.702 g) * (u + 1)) with g = min(W_gate h, limit),
  *           u = clamp(W_up h, -limit, limit); router scores sigmoid(W_router h) in fp32, the `top` largest of score + correction
@@ -444,7 +445,8 @@ int b200_dlm_set_stream(b200_dlm* h, void* stream);
  * "attn_split" (CTAs per attention tile along the keys; 0 = chosen per step), "attn_tc" (0: attention and grouped expert
  * products on the CUDA cores also where a tensor-core kernel would take them; 2: the tensor-core window / sigmoid attention also for
  * single-token requests; at 1 the sigmoid attention takes it for single tokens once a request holds 512 keys), "scan_segment" (before cache_begin; tokens per segment of the recurrences: portions of at least two
- * segments run as segments side by side; default 256), "time_kernels" (CUDA events around every
+ * segments run as segments side by side; default 256), "delta_chunk" (0: the delta rule walks every portion token by token; default 1:
+ * portions of at least 16 tokens run in chunks of 32), "time_kernels" (CUDA events around every
  * operation, summed per class: a step then waits for its own end). */
 int b200_dlm_set_option(b200_dlm* h, const char* name, int value);
 /* Milliseconds spent so far per class of operation under "time_kernels": [0] linears, [1] attention, [2] the small products
