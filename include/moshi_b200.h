@@ -30,7 +30,7 @@
 extern "C" {
 #endif
 
-#define B200_ABI_VERSION 5
+#define B200_ABI_VERSION 6
 
 enum {
   B200_OK = 0,
@@ -371,6 +371,23 @@ int b200_frame_read_buffer(b200_frame* f, const char* name, void* dst_dev, int64
  *           B200_MLP_MOE_CLAMPED_GLU: routed experts W_down (g * sigmoid(1.702 g) * (u + 1)) with g = min(W_gate h, limit),
  *           u = clamp(W_up h, -limit, limit); router scores sigmoid(W_router h) in fp32, the `top` largest of score + correction
  *           are chosen, weighted by score / (sum of the chosen scores) * router_scale
+ * and (the Dibulix design):
+ *   block   B200_BLOCK_PRE_NORM_STREAMS: pre-norm sublayers (mixer, then feed-forward) on `streams` residual streams, all equal
+ *           to the embedding at the start: a sublayer reads u = sum_s in[s] x_s, computes y = f(rms(u) * w), and every stream
+ *           becomes x_t <- sum_s mix[s][t] x_s + out[t] y (from the old streams); streams = 0: one stream, x += y.  The output
+ *           norm reads the sum of the streams; tied_head: the logits are embed . rms(x) * w, times logit_scale
+ *   mixer   B200_MIXER_LATENT_ATTENTION with rot_dims > 0: every head has `dim` unrotated and `rot_dims` rotated query
+ *           dimensions; W_dkv has kv_rank + rot_dims rows, the last rot_dims being one rotated key part shared by the heads
+ *           (not normed); the cache row is [latent | rotated key part]; window > 0: a sliding window; sink B200_SINK_NONE: an
+ *           ordinary softmax; head_gate: head h's result is multiplied by sigmoid((W_g h)_h)
+ *           B200_MIXER_PARALLEL of B200_MIXER_WINDOW_ATTENTION (bias: q, k, v add a bias; sink B200_SINK_UNIT: the denominator
+ *           holds one extra unit; no head mix, no norms, no convolution) and B200_MIXER_MINGRU, summed as a_scale * a + b_scale * b
+ *           B200_MIXER_MINGRU: S <- (1 - z) S + z c element by element over `dim` channels, z = sigmoid(W_z h + b_z),
+ *           c = u + 1/2 where u = W_x h + b_x >= 0 and sigmoid(u) below; the result is W_o (S * silu(W_g h))
+ *           B200_MIXER_CHANNEL_DELTA: B200_MIXER_DELTA with one decay per head and key channel,
+ *           g = exp(-exp(A_log[h]) softplus(W_a2 (W_a1 h) + dt_bias)), acting on the rows of S, and the gate
+ *           sigmoid(W_g2 (W_g1 h)) on the normed result; single tokens and portions run token by token
+ *   mlp     B200_MLP_DENSE_RELU2 on its own norm
  * Precision: compute_dtype B200_BF16 = bf16 weights / activations / cache with fp32 accumulation, while norms, attention
  * scores and weights, gates, routers, recurrent state, the residual stream and the depth average stay fp32; B200_F32 =
  * everything in IEEE fp32 (FMA).
@@ -380,9 +397,11 @@ int b200_frame_read_buffer(b200_frame* f, const char* name, void* dst_dev, int64
 typedef struct b200_dlm b200_dlm;
 
 enum { B200_MIXER_LATENT_ATTENTION = 1, B200_MIXER_WINDOW_ATTENTION = 2, B200_MIXER_GLA = 3, B200_MIXER_MLSTM = 4, B200_MIXER_PARALLEL = 5,
-       B200_MIXER_SIGMOID_ATTENTION = 6, B200_MIXER_RETENTION = 7, B200_MIXER_DELTA = 8 };
+       B200_MIXER_SIGMOID_ATTENTION = 6, B200_MIXER_RETENTION = 7, B200_MIXER_DELTA = 8, B200_MIXER_MINGRU = 9, B200_MIXER_CHANNEL_DELTA = 10 };
 enum { B200_MLP_NONE = 0, B200_MLP_DENSE_RELU2 = 1, B200_MLP_MOE_RELU2 = 2, B200_MLP_DENSE_GATED_GELU = 3, B200_MLP_MOE_CLAMPED_GLU = 4 };
-enum { B200_BLOCK_GATED_DEPTH_AVERAGE = 0, B200_BLOCK_SANDWICH = 1, B200_BLOCK_PARALLEL_RESIDUAL = 2 };
+enum { B200_BLOCK_GATED_DEPTH_AVERAGE = 0, B200_BLOCK_SANDWICH = 1, B200_BLOCK_PARALLEL_RESIDUAL = 2, B200_BLOCK_PRE_NORM_STREAMS = 3 };
+enum { B200_SINK_LEARNED = 0, B200_SINK_NONE = 1, B200_SINK_UNIT = 2 };   /* what a softmax denominator holds beside the keys */
+#define B200_DLM_MAX_STREAMS 8
 enum { B200_ROT_HALVES = 0, B200_ROT_ADJACENT = 1 };          /* rot_pairing: dimension i with i + rot_dims / 2, or 2i with 2i + 1 */
 enum { B200_ROT_PLAIN = 0, B200_ROT_BANDS = 1, B200_ROT_RAMP = 2 };   /* rot_scaling */
 #define B200_DLM_MAX_DECAY_HEADS 256
@@ -406,6 +425,9 @@ typedef struct {
   float softcap;              /* sigmoid attention: cap of the scaled score (<= 0: none)        */
   int v_mix;                  /* sigmoid attention: values blended with the first v_mix layer's */
   const float* decay;         /* retention: [heads] decays (copied by create)                   */
+  int bias;                   /* the q / k / v (minGRU: z / x) projections add a bias           */
+  int sink;                   /* B200_SINK_*                                                    */
+  int head_gate;              /* latent attention: a sigmoid gate per head on the result        */
 } b200_dlm_mixer;
 
 typedef struct {
@@ -416,6 +438,7 @@ typedef struct {
   int experts, top;           /* routed experts and how many of them a token uses               */
   float expert_limit;         /* clamped experts: bound of the gate (above) and of the value (both sides) */
   float router_scale;         /* clamped experts: multiplies the normalised weights             */
+  float a_scale, b_scale;     /* pre-norm streams, PARALLEL: the pair's results are summed with these factors */
 } b200_dlm_layer;
 
 typedef struct {
@@ -426,6 +449,9 @@ typedef struct {
   int canon_taps;             /* sandwich block: taps of the convolution on the mixer's input   */
   float logit_softcap;
   const b200_dlm_layer* layers;
+  int streams;                /* pre-norm streams: residual streams (0: one plain residual, no read / write weights) */
+  float logit_scale;          /* pre-norm streams: multiplies the logits                         */
+  int tied_head;              /* the logits come from the embedding table (no "head" tensor)     */
 } b200_dlm_config;
 
 int b200_dlm_create(const b200_dlm_config* cfg, b200_dlm** out);

@@ -14,7 +14,7 @@ LIB_PATH = Path(__file__).resolve().parent / "_C" / "libmoshi_b200.so"
 
 B200_OK, B200_ERR_INVALID, B200_ERR_SHAPE, B200_ERR_STATE, B200_ERR_CUDA, B200_ERR_MISSING = range(6)
 B200_F32, B200_BF16, B200_F16, B200_I64, B200_U8, B200_I8 = range(6)
-ABI_VERSION = 5
+ABI_VERSION = 6
 
 
 class MimiConfigC(C.Structure):
@@ -46,18 +46,20 @@ class DLMMixerC(C.Structure):
                 ("scale", C.c_float), ("window", C.c_int), ("conv_taps", C.c_int), ("rot_dims", C.c_int), ("rot_base", C.c_float),
                 ("rot_factor", C.c_float), ("rot_low", C.c_float), ("rot_high", C.c_float), ("rot_original", C.c_float),
                 ("gate_cap", C.c_float), ("tau", C.c_float), ("rot_pairing", C.c_int), ("rot_scaling", C.c_int), ("rot_fast", C.c_float),
-                ("rot_slow", C.c_float), ("softcap", C.c_float), ("v_mix", C.c_int), ("decay", C.POINTER(C.c_float))]
+                ("rot_slow", C.c_float), ("softcap", C.c_float), ("v_mix", C.c_int), ("decay", C.POINTER(C.c_float)),
+                ("bias", C.c_int), ("sink", C.c_int), ("head_gate", C.c_int)]
 
 
 class DLMLayerC(C.Structure):
     _fields_ = [("mixer", C.c_int), ("a", DLMMixerC), ("b", DLMMixerC), ("mlp", C.c_int), ("ff", C.c_int), ("experts", C.c_int), ("top", C.c_int),
-                ("expert_limit", C.c_float), ("router_scale", C.c_float)]
+                ("expert_limit", C.c_float), ("router_scale", C.c_float), ("a_scale", C.c_float), ("b_scale", C.c_float)]
 
 
 class DLMConfigC(C.Structure):
     _fields_ = [("vocab", C.c_int), ("width", C.c_int), ("n_layers", C.c_int), ("embedding_scale", C.c_float),
                 ("residual_mult", C.c_float), ("norm_eps", C.c_float), ("compute_dtype", C.c_int), ("block", C.c_int),
-                ("canon_taps", C.c_int), ("logit_softcap", C.c_float), ("layers", C.POINTER(DLMLayerC))]
+                ("canon_taps", C.c_int), ("logit_softcap", C.c_float), ("layers", C.POINTER(DLMLayerC)),
+                ("streams", C.c_int), ("logit_scale", C.c_float), ("tied_head", C.c_int)]
 
 
 _P = C.c_void_p

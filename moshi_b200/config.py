@@ -270,11 +270,12 @@ def tiny_lm_config(**over) -> LMConfig:
 # Decoder LMs given as a list of layers (text-only; no reference counterpart)
 # ---------------------------------------------------------------------------------------------------
 MIXERS = {"latent_attention": 1, "window_attention": 2, "gla": 3, "mlstm": 4, "parallel": 5,    # name -> B200_MIXER_*
-          "sigmoid_attention": 6, "retention": 7, "delta": 8}
+          "sigmoid_attention": 6, "retention": 7, "delta": 8, "mingru": 9, "channel_delta": 10}
 # feed-forward kind -> B200_MLP_*: "dense" / "moe" are the squared-ReLU layers (a null "mlp" = none), "gated_gelu" a gated dense
 # layer with the tanh form of GELU, "moe_clamped_glu" routed experts with clamped gates behind a sigmoid router
 MLP_KINDS = {None: 0, "dense": 1, "moe": 2, "gated_gelu": 3, "moe_clamped_glu": 4}
-BLOCKS = {"gated_depth_average": 0, "sandwich": 1, "parallel_residual": 2}                        # block arrangement -> B200_BLOCK_*
+BLOCKS = {"gated_depth_average": 0, "sandwich": 1, "parallel_residual": 2, "pre_norm_streams": 3}  # block arrangement -> B200_BLOCK_*
+SINKS = {"learned": 0, "none": 1, "unit": 2}                                                      # softmax denominator's extra term -> B200_SINK_*
 ROT_PAIRINGS = {"halves": 0, "adjacent": 1}                                                       # -> B200_ROT_HALVES / B200_ROT_ADJACENT
 ROT_SCALINGS = {None: 0, "bands": 1, "ramp": 2}                                                   # -> B200_ROT_PLAIN / BANDS / RAMP
 
@@ -291,7 +292,13 @@ class MixerConfig:
     ``sigmoid_attention``: causal, weights sigmoid(softcap * tanh(q.k * scale / softcap) + bias) mixed over heads after the sigmoid;
     ``rot_pairing`` "adjacent" turns dimension 2i with 2i + 1; ``rot_scaling_kind`` "ramp" reads ``rot_scaling`` = {factor, original,
     fast, slow}; ``v_mix``: values blended with those of the first such layer.  ``retention``: one fixed ``decay`` per head.
-    ``delta``: gated delta rule behind convolutions of ``conv`` taps, ``kv_heads`` query/key heads shared by ``heads`` value heads."""
+    ``delta``: gated delta rule behind convolutions of ``conv`` taps, ``kv_heads`` query/key heads shared by ``heads`` value heads.
+    ``channel_delta``: the same with one decay per head and key channel through a bottleneck of ``decay_rank``, and a sigmoid
+    output gate through one of ``gate_rank`` (both are tensor shapes, not config keys).  ``mingru``: an element-wise gated
+    recurrence of ``dim`` channels.  ``bias``: the q / k / v (or gate / candidate) projections add a bias.  ``sink``: what the
+    softmax denominator holds beside the keys ("learned": exp of a weight per head, "none", "unit": one).  ``head_gate``: a
+    sigmoid gate per head on the attention's result.  A ``latent_attention`` with ``rot_dims`` > 0 has that many rotated
+    query / key dimensions per head beside its ``dim`` unrotated ones; the rotated key part is one row shared by the heads."""
     kind: str
     heads: int
     dim: int
@@ -312,6 +319,10 @@ class MixerConfig:
     softcap: float = 0.0
     v_mix: bool = False
     decay: tp.Optional[tp.List[float]] = None
+    bias: bool = False
+    sink: str = "learned"
+    head_gate: bool = False
+    gate_rank: int = 16
 
 
 def _window_attention_from_dict(m: dict) -> MixerConfig:
@@ -347,6 +358,8 @@ class DecoderLayerConfig:
     top: int = 0
     expert_limit: float = 0.0
     router_scale: float = 1.0
+    a_scale: float = 1.0                # a parallel pair whose results are summed with constant factors
+    b_scale: float = 1.0
 
     @staticmethod
     def from_dict(d: dict) -> "DecoderLayerConfig":
@@ -394,7 +407,7 @@ class DecoderLayerConfig:
 
     def mixers(self) -> tuple:
         """(a, b) as ``MixerConfig`` whatever the kind (a latent attention's flat fields are wrapped)."""
-        if self.type == "latent_attention":
+        if self.type == "latent_attention" and self.a is None:
             return MixerConfig(kind=self.type, heads=self.heads, dim=self.dim, vdim=self.vdim, kv_rank=self.kv_rank, scale=self.scale), None
         return self.a, self.b
 
@@ -414,6 +427,9 @@ class DecoderLMConfig:
     block: str = "gated_depth_average"
     canon_taps: int = 0
     logit_softcap: float = 0.0
+    streams: int = 0                    # pre_norm_streams: residual streams with learned read / write weights (0: one plain residual)
+    logit_scale: float = 1.0
+    tied_head: bool = False             # the logits come from the embedding table
 
     @staticmethod
     def from_dict(d: dict) -> "DecoderLMConfig":
@@ -629,5 +645,111 @@ class NamalixConfig(DecoderLMConfig):
         return out
 
 
+@dataclass
+class DibulixConfig(DecoderLMConfig):
+    """``config.json`` of the Dibulix design: pre-norm sublayers (mixer, then a dense squared-ReLU feed-forward or none) on
+    ``streams`` residual streams that every sublayer reads as a weighted sum and rewrites through a small mixing matrix; layers of
+    type ``latent_attention`` (a cached latent plus one rotated key part shared by the heads, rotation by halves with the index
+    ramp, a sliding window, a sigmoid gate per head), ``parallel`` (sliding-window attention with biased projections, rotation of
+    adjacent pairs and one extra unit in the softmax denominator, beside a minGRU; summed with constant factors) and
+    ``channel_delta`` (gated delta rule with a decay per key channel); logits from the embedding table times ``logit_scale``."""
+
+    TYPES = ("latent_attention", "parallel", "channel_delta")
+
+    @staticmethod
+    def _layer(i: int, d: dict) -> DecoderLayerConfig:
+        t, m, mlp = d["type"], d["mixer"], d.get("mlp")
+        if t not in DibulixConfig.TYPES:
+            raise ValueError(f"layer {i}: a Dibulix layer is one of {sorted(DibulixConfig.TYPES)}, not {t!r}")
+        if mlp is not None and mlp.get("kind") != "dense":
+            raise ValueError(f"layer {i}: unknown feed-forward kind {mlp.get('kind')!r}")
+        kw: dict = dict(type=t, mlp_kind=None if mlp is None else "dense", ff=0 if mlp is None else int(mlp["ff"]))
+        if t == "latent_attention":
+            rot = dict(m.get("rot") or {})
+            rd = int(m.get("rot_dim", 0))
+            if rd and int(rot.get("dims", rd)) != rd:
+                raise ValueError(f"layer {i}: the rotation covers the rotated part (rot.dims = rot_dim)")
+            rot["dims"] = rd
+            a = MixerConfig(kind=t, heads=int(m["heads"]), dim=int(m["dim"]), vdim=int(m["vdim"]), kv_rank=int(m["kv_rank"]), scale=float(m["scale"]),
+                            window=int((m.get("mask") or {}).get("size", 0)), sink="none", head_gate=True, **_rot_fields({"rot": rot}, "halves"))
+            return DecoderLayerConfig(a=a, **kw)
+        if t == "parallel":
+            l, r = m["left"], m["right"]
+            a = MixerConfig(kind="window_attention", heads=int(l["heads"]), kv_heads=int(l["kv_heads"]), dim=int(l["dim"]), vdim=int(l["vdim"]),
+                            scale=float(l["scale"]), window=int((l.get("mask") or {}).get("size", 0)), bias=True, sink="unit", **_rot_fields(l, "adjacent"))
+            b = MixerConfig(kind="mingru", heads=1, dim=int(r["width"]), vdim=int(r["width"]), bias=True)
+            return DecoderLayerConfig(a=a, b=b, a_scale=float(m.get("left_scale", 1.0)), b_scale=float(m.get("right_scale", 1.0)), **kw)
+        a = MixerConfig(kind=t, heads=int(m["heads"]), kv_heads=int(m["kv_heads"]), dim=int(m["dim"]), vdim=int(m["vdim"]), conv=int(m["conv"]),
+                        decay_rank=int(m.get("decay_rank", 16)), gate_rank=int(m.get("gate_rank", 16)))
+        return DecoderLayerConfig(a=a, **kw)
+
+    @staticmethod
+    def from_dict(d: dict) -> "DibulixConfig":
+        return DibulixConfig(architecture=d["architecture"], vocab=int(d["vocab"]), width=int(d["width"]),
+                             layers=[DibulixConfig._layer(i, x) for i, x in enumerate(d["layers"])], norm_eps=float(d["norm"]["eps"]),
+                             block="pre_norm_streams", streams=int(d.get("streams", 0)), logit_scale=float(d.get("logit_scale", 1.0)), tied_head=True)
+
+    @staticmethod
+    def _layer_to_dict(L: DecoderLayerConfig) -> dict:
+        a = L.a
+        if L.type == "latent_attention":
+            mixer: dict = {"dim": a.dim, "heads": a.heads, "kv_rank": a.kv_rank, "rot_dim": a.rot_dims, "scale": a.scale, "vdim": a.vdim}
+            rot = _rot_to_dict(a)
+            if rot is not None:
+                mixer["rot"] = rot
+            if a.window:
+                mixer["mask"] = {"size": a.window}
+        elif L.type == "parallel":
+            left: dict = {"dim": a.dim, "heads": a.heads, "kv_heads": a.kv_heads, "scale": a.scale, "vdim": a.vdim}
+            rot = _rot_to_dict(a)
+            if rot is not None:
+                left["rot"] = rot
+            if a.window:
+                left["mask"] = {"size": a.window}
+            mixer = {"left": left, "left_scale": L.a_scale, "right": {"width": L.b.dim}, "right_scale": L.b_scale}
+        else:
+            mixer = {"conv": a.conv, "dim": a.dim, "heads": a.heads, "kv_heads": a.kv_heads, "vdim": a.vdim}
+        return {"mixer": mixer, "mlp": None if L.mlp_kind is None else {"ff": L.ff, "kind": "dense"}, "type": L.type}
+
+    def to_dict(self) -> dict:
+        d = {"architecture": self.architecture, "layers": [self._layer_to_dict(x) for x in self.layers], "logit_scale": self.logit_scale,
+             "norm": {"eps": self.norm_eps}, "vocab": self.vocab, "width": self.width}
+        if self.streams:
+            d["streams"] = self.streams
+        return d
+
+    def tensor_shapes(self) -> dict:
+        W, s = self.width, self.streams
+        out = {"embed": (self.vocab, W)}
+        for i, L in enumerate(self.layers):
+            p, m, a = f"l{i}.", f"l{i}.mix.", L.a
+            out[p + "norm1"] = (W,)
+            if L.mlp_kind is not None:
+                out[p + "norm2"] = (W,)
+            if L.type == "latent_attention":
+                out.update({m + "q": (a.heads * (a.dim + a.rot_dims), W), m + "dkv": (a.kv_rank + a.rot_dims, W), m + "dkv.norm": (a.kv_rank,),
+                            m + "uk": (a.heads * a.dim, a.kv_rank), m + "uv": (a.heads * a.vdim, a.kv_rank), m + "g": (a.heads, W),
+                            m + "o": (W, a.heads * a.vdim)})
+            elif L.type == "parallel":
+                l, r, n = m + "left.", m + "right.", L.b.dim
+                for nm, rows in (("q", a.heads * a.dim), ("k", a.kv_heads * a.dim), ("v", a.kv_heads * a.vdim)):
+                    out.update({l + nm: (rows, W), l + nm + ".b": (rows,)})
+                out.update({l + "o": (W, a.heads * a.vdim), r + "z": (n, W), r + "z.b": (n,), r + "x": (n, W), r + "x.b": (n,), r + "g": (n, W),
+                            r + "o": (W, n)})
+            else:
+                nq, nv, nd = a.kv_heads * a.dim, a.heads * a.vdim, a.heads * a.dim
+                out.update({m + "q": (nq, W), m + "q.conv": (nq, a.conv), m + "k": (nq, W), m + "k.conv": (nq, a.conv), m + "v": (nv, W),
+                            m + "v.conv": (nv, a.conv), m + "b": (a.heads, W), m + "A_log": (a.heads,), m + "norm": (a.vdim,),
+                            m + "a1": (a.decay_rank, W), m + "a2": (nd, a.decay_rank), m + "dt_bias": (nd,), m + "g1": (a.gate_rank, W),
+                            m + "g2": (nv, a.gate_rank), m + "o": (W, nv)})
+            if L.mlp_kind is not None:
+                out.update({p + "mlp.up": (L.ff, W), p + "mlp.down": (W, L.ff)})
+            for q in (1, 2) if L.mlp_kind is not None else (1,):
+                if s:
+                    out.update({p + f"hc{q}.in": (s,), p + f"hc{q}.out": (s,), p + f"hc{q}.mix": (s, s)})
+        out["final.norm"] = (W,)
+        return out
+
+
 # architecture name in config.json -> configuration class (the model registry of the text-only decoder LMs)
-DECODER_ARCHITECTURES: dict = {"Likosun": DecoderLMConfig, "Govuvik": GovuvikConfig, "Namalix": NamalixConfig}
+DECODER_ARCHITECTURES: dict = {"Likosun": DecoderLMConfig, "Govuvik": GovuvikConfig, "Namalix": NamalixConfig, "Dibulix": DibulixConfig}

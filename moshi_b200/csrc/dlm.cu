@@ -11,6 +11,7 @@
 #include "dlm_kernels.cuh"
 #include "dlm_mixers.cuh"
 #include "dlm_mixers2.cuh"
+#include "dlm_mixers3.cuh"
 #include "gemm_sk.cuh"
 #include "lm_kernels.cuh"
 
@@ -62,6 +63,15 @@ struct Layer {
   float *pbias = nullptr, *vlambda = nullptr, *head_decay = nullptr, *A_log = nullptr, *dt_bias = nullptr, *correction = nullptr;
   float rot_amp = 1.f;
   std::vector<float> decay;            // retention: the configuration's decays (copied at create)
+  // ---- pre-norm streams block: mixer and feed-forward on norms of their own; per sublayer the read, write and mixing weights of
+  // the residual streams.  Latent attention with a rotated part: cache rows of rp elements [latent | rotated key part | padding].
+  // Parallel pair: window attention (a) beside a minGRU (b), projection [q | k | v | z | x | g].  Channel delta: [q | k | v | a1 | g1].
+  float *hc_in[2] = {nullptr, nullptr}, *hc_out[2] = {nullptr, nullptr}, *hc_mix[2] = {nullptr, nullptr};
+  Weight up;
+  int rp = 0;
+  int g_z = 0, g_x = 0, g_g = 0, c_a1 = 0, c_g1 = 0, gate_rank = 0;
+  float *qkv_bias = nullptr, *zx_bias = nullptr, *gru = nullptr;      // gru: [slots][channels] state of the minGRU
+  void* g2 = nullptr;                  // T [heads * vdim][gate_rank]
 };
 
 // attention tile list of one (heads, rows per tile) combination
@@ -124,6 +134,7 @@ struct b200_dlm {
   float* gram = nullptr;               // [chunks][heads][2 DELTA_CH + 2 DELTA_CH^2]
   int vmix_first = -1;                 // the first attention layer that blends values: the later ones blend its values in
   float* small32 = nullptr;            // [tokens][nsmall] fp32 results of the small projection
+  float* xs = nullptr;                 // pre-norm streams block: the residual streams [tokens][streams][width]
   void *vfirst = nullptr, *act2 = nullptr;      // T [tokens][G * vdim] values of layer vmix_first; T [tokens * top][2 ff] experts' first product
 };
 
@@ -292,7 +303,7 @@ int run_attention(cudaStream_t st, AttnParams p, int tiles, int rpt, bool tensor
   else if (r <= 512) B200_TRY((launch_attn<T, 16, 4>(st, p, tiles, p.nsplit)));
   else B200_TRY((launch_attn<T, 32, 2>(st, p, tiles, p.nsplit)));
   if (p.nsplit > 1) {
-    B200_LAUNCH(latent_attn_merge_kernel, dim3(tiles, rpt), 128, 0, st, p.part, p.tile_row0, p.tile_rows, p.out, r, p.nsplit, rpt);
+    B200_LAUNCH(latent_attn_merge_kernel, dim3(tiles, rpt), 128, 0, st, p.part, p.tile_row0, p.tile_rows, p.out, r, p.nsplit, rpt, p.gate, p.ldg, p.H);
     B200_TRY(check_launch("latent_attn_merge"));
   }
   return B200_OK;
@@ -440,6 +451,36 @@ int add_sig(b200_dlm* h, int H, int rpt) {
   return (int)h->sigs.size() - 1;
 }
 
+// which window attention kernels a layer's head shapes take: the tile of query tokens and of keys that fits shared memory for
+// the CUDA-core kernel (also with tiles of one token, for single-token steps), and the tensor-core kernel when it fits
+int plan_window_attention(b200_dlm* h, Layer& L, int i) {
+  const b200_dlm_mixer& a = L.c.a;
+  const size_t es = esize(h);
+  L.QT = 0;
+  for (int kt : {32, 16, 8}) {
+    for (int qt : {4, 2, 1}) {
+      int ks = 0;
+      const size_t sm = window_attn_smem(a, qt, kt, es, &ks);
+      if (sm <= 200 * 1024) { L.QT = qt; L.KT = kt; L.kstride = ks; L.attn_smem = sm; break; }
+    }
+    if (L.QT) break;
+  }
+  if (!L.QT) B200_FAIL(B200_ERR_SHAPE, "decoder LM: layer %d: the window attention's heads do not fit shared memory", i);
+  L.sig = add_sig(h, a.heads, L.QT * a.heads);
+  for (int kt : {32, 16, 8}) {
+    int ks = 0;
+    const size_t sm = window_attn_smem(a, 1, kt, es, &ks);
+    if (sm <= 200 * 1024) { L.sig_one = add_sig(h, a.heads, a.heads); L.KT_one = kt; L.kstride_one = ks; L.smem_one = sm; break; }
+  }
+  if (!h->f32 && a.dim % 16 == 0 && a.vdim % 16 == 0) {     // bf16 cache, fragment-sized heads: the tensor-core kernel, if it fits
+    const size_t Hh = a.heads, QS = L.Nq + 8, KS = L.Nk + 8, VS = L.Nv + 8;
+    const size_t sm = 2 * (16 * QS + 32 * KS + 32 * VS + Hh * 16 * 40) + 4 * (Hh * 16 * 40 + Hh * std::max<size_t>(Hh, 16) + 3 * Hh * 16);
+    const int items = ceil_div(a.heads * ceil_div(a.vdim, 64), 8);
+    if (sm <= 220 * 1024 && items <= 4) { L.sig_mma = add_sig(h, a.heads, 16 * a.heads); L.mma_items = items <= 2 ? items : 4; L.mma_smem = sm; }
+  }
+  return B200_OK;
+}
+
 int finalize_sandwich_layer(b200_dlm* h, int i, std::vector<void*>& drop) {
   Layer& L = h->layers[i];
   const b200_dlm_config& c = h->cfg;
@@ -510,29 +551,7 @@ int finalize_sandwich_layer(b200_dlm* h, int i, std::vector<void*>& drop) {
     B200_TRY(seal_weight(h, L.a_o, wo, (int)W, a.heads * a.vdim, drop, (int)W));
     B200_TRY(get_f32(h, l + "out", W, &L.a_out));
     B200_TRY(get_f32(h, r + "out", W, &L.b_out));
-    // tile of query tokens and of keys that fits shared memory
-    L.QT = 0;
-    for (int kt : {32, 16, 8}) {
-      for (int qt : {4, 2, 1}) {
-        int ks = 0;
-        const size_t sm = window_attn_smem(a, qt, kt, es, &ks);
-        if (sm <= 200 * 1024) { L.QT = qt; L.KT = kt; L.kstride = ks; L.attn_smem = sm; break; }
-      }
-      if (L.QT) break;
-    }
-    if (!L.QT) B200_FAIL(B200_ERR_SHAPE, "decoder LM: layer %d: the window attention's heads do not fit shared memory", i);
-    L.sig = add_sig(h, a.heads, L.QT * a.heads);
-    for (int kt : {32, 16, 8}) {
-      int ks = 0;
-      const size_t sm = window_attn_smem(a, 1, kt, es, &ks);
-      if (sm <= 200 * 1024) { L.sig_one = add_sig(h, a.heads, a.heads); L.KT_one = kt; L.kstride_one = ks; L.smem_one = sm; break; }
-    }
-    if (!h->f32 && a.dim % 16 == 0 && a.vdim % 16 == 0) {     // bf16 cache, fragment-sized heads: the tensor-core kernel, if it fits
-      const size_t Hh = a.heads, QS = L.Nq + 8, KS = L.Nk + 8, VS = L.Nv + 8;
-      const size_t sm = 2 * (16 * QS + 32 * KS + 32 * VS + Hh * 16 * 40) + 4 * (Hh * 16 * 40 + Hh * std::max<size_t>(Hh, 16) + 3 * Hh * 16);
-      const int items = ceil_div(a.heads * ceil_div(a.vdim, 64), 8);
-      if (sm <= 220 * 1024 && items <= 4) { L.sig_mma = add_sig(h, a.heads, 16 * a.heads); L.mma_items = items <= 2 ? items : 4; L.mma_smem = sm; }
-    }
+    B200_TRY(plan_window_attention(h, L, i));
     // right: gated linear attention
     B200_TRY(matrix(r + "a2", Rq, L.decay_rank, &L.a2));
     B200_TRY(get_f32(h, r + "a2.b", Rq, &L.a2b));
@@ -638,7 +657,7 @@ ScanLayout scan_layout(b200_dlm* h, ScanParams& p, bool whole) {
   L.rows = L.wide ? (p.dim <= 64 ? 4 : p.dim <= 128 ? 8 : 16) : (p.dim <= 32 ? 4 : p.dim <= 64 ? 8 : p.dim <= 128 ? 16 : 32);
   p.lpc = L.lanes4 ? lpc : 0; p.rows = L.rows;
   const int Dp = L.lanes4 ? lpc * L.rows : p.dim;
-  p.prow = ((MODE == MODE_DECAY ? 3 : 2) * Dp + (MODE == MODE_DECAY ? 0 : 2) + 3) / 4 * 4;
+  p.prow = ((MODE == MODE_DECAY || MODE == MODE_CHDELTA ? 3 : 2) * Dp + (MODE == MODE_DECAY ? 0 : 2) + 3) / 4 * 4;
   return L;
 }
 
@@ -665,7 +684,7 @@ int scan_run(b200_dlm* h, const ScanParams& p, const ScanLayout& L, bool whole) 
     else rc = launch_scan_r<MODE, 32, 8, 1>(st, p, nu);
   }
   B200_TRY(rc);
-  if constexpr (MODE != MODE_DELTA) {
+  if constexpr (MODE != MODE_DELTA && MODE != MODE_CHDELTA) {
   bool any = false;
   for (auto& u : h->units) any |= u.buf >= 0;
   if (!any || whole) return B200_OK;
@@ -712,7 +731,7 @@ int launch_scan(b200_dlm* h, ScanParams p, int n_tok) {
 }
 
 template <typename T>
-int window_attention(b200_dlm* h, const Layer& L, int n_tok, int max_ctx) {
+int window_attention(b200_dlm* h, const Layer& L, int n_tok, int max_ctx, long long ldq = 0) {      // ldq: row stride of the fp32 queries (0: q, k, v side by side)
   const b200_dlm_mixer& a = L.c.a;
   bool mma = false;
   if constexpr (sizeof(T) == 2) mma = h->attn_tc && L.sig_mma >= 0 && (h->max_entry_tokens > 1 || h->attn_tc > 1);      // single tokens: a 16-row fragment tile would be all padding
@@ -728,7 +747,7 @@ int window_attention(b200_dlm* h, const Layer& L, int n_tok, int max_ctx) {
     attr_set = true;
   }
   WindowAttnParams p;
-  p.q = h->qkv32; p.ldq = L.Nq + L.Nk + L.Nv; p.kcache = L.kcache; p.vcache = L.vcache; p.mix = L.mixhh; p.sink = L.sink;
+  p.q = h->qkv32; p.ldq = ldq > 0 ? ldq : L.Nq + L.Nk + L.Nv; p.kcache = L.kcache; p.vcache = L.vcache; p.mix = L.mixhh; p.sink = L.sink;
   p.tile_row0 = h->meta_dev + s.off_row0; p.tile_rows = h->meta_dev + s.off_rows; p.tile_slot = h->meta_dev + s.off_slot;
   p.tok_pos = h->meta_dev + h->off_pos; p.out = h->obuf; p.part = h->part;
   p.cap = h->cap; p.H = a.heads; p.G = a.kv_heads; p.dim = a.dim; p.vdim = a.vdim; p.window = a.window; p.QT = QT; p.KT = KT; p.kstride = one ? L.kstride_one : L.kstride;
@@ -1314,6 +1333,323 @@ int step_parallel(b200_dlm* h, int n_tok, int n_want, int max_ctx, float* logits
   return check_launch("decoder LM step");
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Pre-norm sublayers on residual streams: u = sum_s in[s] x_s;  y = f(rms(u) * w);  x_t <- sum_s mix[s][t] x_s + out[t] y
+// ---------------------------------------------------------------------------------------------------------------------------
+
+int finalize_streams_layer(b200_dlm* h, int i, std::vector<void*>& drop) {
+  Layer& L = h->layers[i];
+  const b200_dlm_config& c = h->cfg;
+  const b200_dlm_mixer &a = L.c.a, &b = L.c.b;
+  const int64_t W = c.width;
+  const size_t es = esize(h);
+  const std::string p = "l" + std::to_string(i) + ".", m = p + "mix.";
+  const bool mlp = L.c.mlp != B200_MLP_NONE;
+  auto matrix = [&](const std::string& name, int64_t rows, int64_t K, void** out) -> int {
+    B200_TRY(h->weights.alloc(out, (size_t)rows * K * es, false));
+    return put_matrix(h, name, rows, K, *out);
+  };
+  auto sealed = [&](const std::string& name, int64_t rows, int64_t K, Weight& w, int ld_out) -> int {
+    void* rm = nullptr;
+    B200_TRY(matrix(name, rows, K, &rm));
+    return seal_weight(h, w, rm, (int)rows, (int)K, drop, ld_out);
+  };
+  B200_TRY(get_f32(h, p + "norm1", W, &L.n1w));
+  if (mlp) B200_TRY(get_f32(h, p + "norm2", W, &L.n2w));
+  for (int q = 0; q < (mlp ? 2 : 1) && c.streams > 0; ++q) {
+    const std::string hc = p + "hc" + std::to_string(q + 1) + ".";
+    B200_TRY(get_f32(h, hc + "in", c.streams, &L.hc_in[q]));
+    B200_TRY(get_f32(h, hc + "out", c.streams, &L.hc_out[q]));
+    B200_TRY(get_f32_shaped(h, hc + "mix", {c.streams, c.streams}, &L.hc_mix[q]));
+  }
+  void* cat = nullptr;
+  auto at = [&](int off) { return static_cast<char*>(cat) + (size_t)off * W * es; };
+  auto pad8 = [](int v) { return (v + 7) / 8 * 8; };
+  auto frequencies = [&](const b200_dlm_mixer& mx) -> int {
+    if (mx.rot_dims <= 0) return B200_OK;
+    std::vector<double> fr;
+    if (mx.rot_scaling == B200_ROT_RAMP) fr = rotary_frequencies_ramp(mx, &L.rot_amp);
+    else fr = rotary_frequencies(mx);
+    B200_TRY(h->weights.alloc_t(&L.freq, fr.size(), false));
+    B200_CUDA(cudaMemcpy(L.freq, fr.data(), fr.size() * sizeof(double), cudaMemcpyHostToDevice));
+    return B200_OK;
+  };
+  if (L.c.mixer == B200_MIXER_LATENT_ATTENTION) {
+    const int64_t H = a.heads, dq = a.dim + a.rot_dims, r = a.kv_rank, rd = a.rot_dims;
+    L.Nq = (int)(H * dq);
+    L.off_q = 0; L.off_dkv = pad8(L.Nq); L.ncat = L.off_dkv + (int)(r + rd);
+    L.ldp = pad8(L.ncat);
+    L.rp = pad8((int)(r + rd));
+    B200_TRY(h->weights.alloc(&cat, (size_t)L.ncat * W * es, true));
+    B200_TRY(put_matrix(h, m + "q", H * dq, W, at(L.off_q)));
+    B200_TRY(put_matrix(h, m + "dkv", r + rd, W, at(L.off_dkv)));
+    B200_TRY(seal_weight(h, L.cat, cat, L.ncat, (int)W, drop));
+    B200_TRY(get_f32(h, m + "dkv.norm", r, &L.cnorm));
+    if (a.head_gate) {
+      L.nsmall = (int)H; L.s_gate = 0;
+      B200_TRY(matrix(m + "g", H, W, &L.w_small));
+      h->weight_bytes += H * W * es;
+    }
+    if (a.sink == B200_SINK_LEARNED) B200_TRY(get_f32(h, m + "sink", H, &L.sink));
+    else if (a.sink == B200_SINK_UNIT) B200_TRY(h->weights.alloc_t(&L.sink, (size_t)H, true));
+    {   // W_uk [H * dim][r] -> per head [r][dim]
+      void* uk = nullptr;
+      B200_TRY(matrix(m + "uk", H * a.dim, r, &uk));
+      B200_TRY(h->weights.alloc(&L.ukT, (size_t)H * a.dim * r * es, false));
+      const long long n = H * a.dim * r;
+      if (h->f32) B200_LAUNCH(head_transpose_kernel<float>, (unsigned)ceil_div64(n, 256), 256, 0, nullptr, static_cast<const float*>(uk), static_cast<float*>(L.ukT), (int)H, a.dim, (int)r);
+      else B200_LAUNCH(head_transpose_kernel<bf16>, (unsigned)ceil_div64(n, 256), 256, 0, nullptr, static_cast<const bf16*>(uk), static_cast<bf16*>(L.ukT), (int)H, a.dim, (int)r);
+      B200_TRY(check_launch("head_transpose"));
+      drop.push_back(uk);
+      h->weight_bytes += n * es;
+    }
+    B200_TRY(matrix(m + "uv", H * a.vdim, r, &L.uv));
+    h->weight_bytes += H * a.vdim * r * es;
+    B200_TRY(sealed(m + "o", W, H * a.vdim, L.o, (int)W));
+    B200_TRY(frequencies(a));
+    L.sig = add_sig(h, (int)H, rows_per_tile(L.rp));
+  } else if (L.c.mixer == B200_MIXER_PARALLEL) {
+    const std::string l = m + "left.", r = m + "right.";
+    const int N = b.dim;
+    L.Nq = a.heads * a.dim; L.Nk = a.kv_heads * a.dim; L.Nv = a.kv_heads * a.vdim;
+    L.p_q = 0; L.p_k = L.Nq; L.p_v = L.p_k + L.Nk; L.g_z = L.p_v + L.Nv; L.g_x = L.g_z + N; L.g_g = L.g_x + N; L.ncat = L.g_g + N;
+    L.ldp = pad8(L.ncat);
+    B200_TRY(h->weights.alloc(&cat, (size_t)L.ncat * W * es, false));
+    B200_TRY(put_matrix(h, l + "q", L.Nq, W, at(L.p_q)));
+    B200_TRY(put_matrix(h, l + "k", L.Nk, W, at(L.p_k)));
+    B200_TRY(put_matrix(h, l + "v", L.Nv, W, at(L.p_v)));
+    B200_TRY(put_matrix(h, r + "z", N, W, at(L.g_z)));
+    B200_TRY(put_matrix(h, r + "x", N, W, at(L.g_x)));
+    B200_TRY(put_matrix(h, r + "g", N, W, at(L.g_g)));
+    B200_TRY(seal_weight(h, L.cat, cat, L.ncat, (int)W, drop));
+    if (a.bias) {
+      const int C = L.Nq + L.Nk + L.Nv;
+      B200_TRY(h->weights.alloc_t(&L.qkv_bias, (size_t)C, false));
+      const Tensor* t = nullptr;
+      int off = 0;
+      for (const char* nm : {"q", "k", "v"}) {
+        const int rows = nm[0] == 'q' ? L.Nq : nm[0] == 'k' ? L.Nk : L.Nv;
+        B200_TRY(find_tensor(h, l + nm + ".b", {rows}, &t));
+        B200_TRY(convert_into(t, L.qkv_bias + off));
+        off += rows;
+      }
+      h->weight_bytes += (int64_t)C * 4;
+    }
+    if (b.bias) {
+      B200_TRY(h->weights.alloc_t(&L.zx_bias, (size_t)2 * N, false));
+      const Tensor* t = nullptr;
+      B200_TRY(find_tensor(h, r + "z.b", {N}, &t));
+      B200_TRY(convert_into(t, L.zx_bias));
+      B200_TRY(find_tensor(h, r + "x.b", {N}, &t));
+      B200_TRY(convert_into(t, L.zx_bias + N));
+      h->weight_bytes += (int64_t)2 * N * 4;
+    }
+    // the score scale goes into the rotated queries; the head mix of the kernel is the identity
+    B200_TRY(h->weights.alloc_t(&L.mixhh, (size_t)a.heads * a.heads, false));
+    B200_LAUNCH(identity_kernel, ceil_div(a.heads * a.heads, 256), 256, 0, nullptr, L.mixhh, a.heads);
+    B200_TRY(check_launch("identity"));
+    if (a.sink == B200_SINK_LEARNED) B200_TRY(get_f32(h, l + "sink", a.heads, &L.sink));
+    else B200_TRY(h->weights.alloc_t(&L.sink, (size_t)a.heads, true));      // a unit in the denominator = a sink of logit 0
+    B200_TRY(frequencies(a));
+    B200_TRY(sealed(l + "o", W, (int64_t)a.heads * a.vdim, L.a_o, (int)W));
+    B200_TRY(sealed(r + "o", W, N, L.r_o, (int)W));
+    B200_TRY(plan_window_attention(h, L, i));
+  } else {      // B200_MIXER_CHANNEL_DELTA
+    const int H = a.heads, G = a.kv_heads, taps = a.conv_taps;
+    L.Nq = G * a.dim; L.Nk = G * a.dim; L.Nv = H * a.vdim;
+    const int Nd = H * a.dim;
+    const Tensor *a1 = h->store.find(m + "a1"), *g1 = h->store.find(m + "g1");
+    if (!a1 || a1->shape.size() != 2 || a1->shape[1] != W || !g1 || g1->shape.size() != 2 || g1->shape[1] != W)
+      B200_FAIL(B200_ERR_MISSING, "decoder LM finalize: tensors '%sa1' / '%sg1' [rank, width] were not loaded", m.c_str(), m.c_str());
+    L.decay_rank = (int)a1->shape[0]; L.gate_rank = (int)g1->shape[0];
+    L.p_q = 0; L.p_k = L.Nq; L.p_v = L.p_k + L.Nk; L.c_a1 = pad8(L.p_v + L.Nv); L.c_g1 = pad8(L.c_a1 + L.decay_rank); L.ncat = L.c_g1 + L.gate_rank;
+    L.ldp = pad8(L.ncat);
+    B200_TRY(h->weights.alloc(&cat, (size_t)L.ncat * W * es, true));
+    B200_TRY(put_matrix(h, m + "q", L.Nq, W, at(L.p_q)));
+    B200_TRY(put_matrix(h, m + "k", L.Nk, W, at(L.p_k)));
+    B200_TRY(put_matrix(h, m + "v", L.Nv, W, at(L.p_v)));
+    B200_TRY(put_matrix(h, m + "a1", L.decay_rank, W, at(L.c_a1)));
+    B200_TRY(put_matrix(h, m + "g1", L.gate_rank, W, at(L.c_g1)));
+    B200_TRY(seal_weight(h, L.cat, cat, L.ncat, (int)W, drop));
+    L.nsmall = H; L.s_ba = 0;
+    B200_TRY(matrix(m + "b", H, W, &L.w_small));
+    h->weight_bytes += (int64_t)H * W * es;
+    B200_TRY(matrix(m + "a2", Nd, L.decay_rank, &L.a2));
+    B200_TRY(matrix(m + "g2", L.Nv, L.gate_rank, &L.g2));
+    h->weight_bytes += ((int64_t)Nd * L.decay_rank + (int64_t)L.Nv * L.gate_rank) * es;
+    const int C = 2 * L.Nq + L.Nv;
+    B200_TRY(h->weights.alloc_t(&L.qkv_conv, (size_t)C * taps, false));
+    const Tensor* t = nullptr;
+    int off = 0;
+    for (const char* nm : {"q", "k", "v"}) {
+      const int rows = nm[0] == 'v' ? L.Nv : L.Nq;
+      B200_TRY(find_tensor(h, m + nm + ".conv", {rows, taps}, &t));
+      B200_TRY(convert_into(t, L.qkv_conv + (size_t)off * taps));
+      off += rows;
+    }
+    h->weight_bytes += (int64_t)C * taps * 4;
+    B200_TRY(get_f32(h, m + "A_log", H, &L.A_log));
+    B200_TRY(get_f32(h, m + "dt_bias", Nd, &L.dt_bias));
+    B200_TRY(get_f32(h, m + "norm", a.vdim, &L.rnorm));
+    B200_TRY(sealed(m + "o", W, L.Nv, L.o, (int)W));
+  }
+  if (mlp) {
+    B200_TRY(sealed(p + "mlp.up", L.c.ff, W, L.up, L.c.ff));
+    B200_TRY(sealed(p + "mlp.down", W, L.c.ff, L.down, (int)W));
+  }
+  return B200_OK;
+}
+
+// the end of a sublayer for any number of streams (a plain residual counts as one stream without weights)
+template <typename T>
+int streams_end(b200_dlm* h, const T* y0, float s0, const T* y1, float s1, const float* mix, const float* out, float* trace, float* xsum,
+                const float* in_next, const float* w_next, int n_tok) {
+  const int W = h->cfg.width, S = std::max(h->cfg.streams, 1);
+  const size_t sm = (size_t)W * 4;
+  T* hb = static_cast<T*>(h->hbuf);
+#define B200_STREAMS_CASE(N) case N: B200_LAUNCH((streams_end_kernel<T, N>), n_tok, 256, sm, h->stream, h->xs, y0, s0, y1, s1, mix, out, trace, xsum, in_next, w_next, hb, W, h->cfg.norm_eps); break;
+  switch (S) {
+    B200_STREAMS_CASE(1) B200_STREAMS_CASE(2) B200_STREAMS_CASE(3) B200_STREAMS_CASE(4) B200_STREAMS_CASE(5) B200_STREAMS_CASE(6) B200_STREAMS_CASE(7)
+    default: B200_LAUNCH((streams_end_kernel<T, 8>), n_tok, 256, sm, h->stream, h->xs, y0, s0, y1, s1, mix, out, trace, xsum, in_next, w_next, hb, W, h->cfg.norm_eps);
+  }
+#undef B200_STREAMS_CASE
+  return check_launch("streams_end");
+}
+
+// latent attention over cache rows [latent | rotated key part]: the queries' first r elements are folded through W_uk, the rest
+// are the rotated query part; the sums over the rows' first r elements go through W_uv
+template <typename T>
+int latent_rope_attention(b200_dlm* h, const Layer& L, int n_tok, int max_ctx) {
+  const b200_dlm_mixer& a = L.c.a;
+  const int H = a.heads, dk = a.dim, dv = a.vdim, r = a.kv_rank, rd = a.rot_dims, rp = L.rp;
+  cudaStream_t st = h->stream;
+  const int* meta = h->meta_dev;
+  T* proj = static_cast<T*>(h->proj);
+  TIMED(CLS_ELEMENTWISE, B200_LAUNCH(latent_rope_append_kernel<T>, n_tok, 128, (size_t)rd * 4 + 4, st, proj, (long long)L.ldp, L.off_q, L.off_dkv, L.cnorm,
+                                     static_cast<T*>(L.cache), h->cap, r, rd, rp, H, dk, a.rot_pairing == B200_ROT_ADJACENT, L.freq, L.rot_amp, a.scale, h->qa,
+                                     meta + h->off_slot, meta + h->off_pos, h->cfg.norm_eps));
+  TIMED(CLS_FOLD, B200_TRY(head_gemm(st, proj + L.off_q, (long long)L.ldp, (long long)(dk + rd), static_cast<const T*>(L.ukT), (long long)dk, (long long)r * dk, h->qa,
+                                     (long long)H * rp, (long long)rp, n_tok, r, dk, H, a.scale, h->attn_tc != 0)));
+  const TileSig& s = h->sigs[L.sig];
+  AttnParams p;
+  p.qa = h->qa; p.cache = L.cache; p.sink = a.sink == B200_SINK_NONE ? nullptr : L.sink;
+  p.tile_row0 = meta + s.off_row0; p.tile_rows = meta + s.off_rows; p.tile_slot = meta + s.off_slot;
+  p.tok_pos = meta + h->off_pos;
+  p.out = h->ol; p.part = h->part; p.cap = h->cap; p.r = rp; p.H = H; p.err = h->err;
+  p.window = a.window;
+  if (a.head_gate) { p.gate = h->small32 + L.s_gate; p.ldg = L.nsmall; }
+  const int seen = a.window > 0 ? std::min(max_ctx, a.window + 32) : max_ctx;
+  p.nsplit = pick_split(h->attn_split, s.count, seen, s.rpt, rp, h->part_floats);
+  TIMED(CLS_ATTN, B200_TRY(run_attention<T>(st, p, s.count, s.rpt, false)));
+  T* ob = static_cast<T*>(h->obuf);
+  TIMED(CLS_FOLD, B200_TRY(head_gemm(st, h->ol, (long long)H * rp, (long long)rp, static_cast<const T*>(L.uv), (long long)r, (long long)dv * r, ob, (long long)H * dv,
+                                     (long long)dv, n_tok, dv, r, H, 1.f, h->attn_tc != 0)));
+  return B200_OK;
+}
+
+template <typename T>
+int step_streams(b200_dlm* h, int n_tok, int n_want, int max_ctx, float* logits_out) {
+  const b200_dlm_config& c = h->cfg;
+  const int W = c.width, S = std::max(c.streams, 1);
+  cudaStream_t st = h->stream;
+  const int* meta = h->meta_dev;
+  const int *tok_slot = meta + h->off_slot, *tok_pos = meta + h->off_pos, *tok_first = meta + h->off_first, *tok_last = meta + h->off_last;
+  const long long stride = (long long)h->tmax * W;
+  T* hb = static_cast<T*>(h->hbuf);
+  T* proj = static_cast<T*>(h->proj);
+  T* ob = static_cast<T*>(h->obuf);
+  T* ob2 = static_cast<T*>(h->obuf2);
+  T* mixo = static_cast<T*>(h->mixo);
+  T* mixo2 = static_cast<T*>(h->mixo2);
+  TIMED(CLS_ELEMENTWISE, B200_LAUNCH(embed_streams_kernel<T>, n_tok, 256, (size_t)W * 4, st, meta + h->off_tok, static_cast<const T*>(h->embed), c.vocab, W, S,
+                                     h->layers[0].hc_in[0], h->layers[0].n1w, h->xs, hb, c.norm_eps, h->err));
+  for (int li = 0; li < c.n_layers; ++li) {
+    const Layer& L = h->layers[li];
+    const b200_dlm_mixer &a = L.c.a, &b = L.c.b;
+    const bool last = li + 1 == c.n_layers, mlp = L.c.mlp != B200_MLP_NONE;
+    TIMED(CLS_LINEAR, B200_TRY(linear<T>(h, hb, W, L.cat, proj, L.ldp, n_tok)));
+    if (L.nsmall) TIMED(CLS_FOLD, B200_TRY(small_proj<T>(h, hb, W, L.w_small, nullptr, h->small32, n_tok, L.nsmall, W)));
+    const T* y1 = nullptr;
+    float s0 = 1.f, s1 = 0.f;
+    if (L.c.mixer == B200_MIXER_LATENT_ATTENTION) {
+      B200_TRY(latent_rope_attention<T>(h, L, n_tok, max_ctx));
+      TIMED(CLS_LINEAR, B200_TRY(linear<T>(h, ob, (long long)a.heads * a.vdim, L.o, mixo, W, n_tok)));
+    } else if (L.c.mixer == B200_MIXER_PARALLEL) {
+      // left: bias, rotation and score scale on the queries (fp32), keys and values into the cache, then the window attention
+      TIMED(CLS_ELEMENTWISE, B200_LAUNCH(attn_rope_cache_kernel<T>, n_tok, 256, (size_t)a.rot_dims * 4 + 4, st, proj, (long long)L.ldp, L.p_q, L.p_k, L.p_v, L.Nq, L.Nk, L.Nv,
+                                         a.dim, a.rot_dims / 2, a.rot_pairing == B200_ROT_ADJACENT, L.freq, L.rot_amp, a.scale, h->qkv32, static_cast<T*>(L.kcache),
+                                         static_cast<T*>(L.vcache), h->cap, tok_slot, tok_pos, (const T*)nullptr, (const float*)nullptr, (T*)nullptr, L.qkv_bias));
+      TIMED(CLS_ATTN, B200_TRY(window_attention<T>(h, L, n_tok, max_ctx, L.Nq)));
+      TIMED(CLS_LINEAR, B200_TRY(linear<T>(h, ob, (long long)a.heads * a.vdim, L.a_o, mixo, W, n_tok)));
+      // right: the minGRU
+      const int N = b.dim;
+      TIMED(CLS_RECURRENT, B200_LAUNCH(mingru_kernel<T>, dim3(ceil_div(N, 128), h->n_entries), 128, 0, st, proj, (long long)L.ldp, L.g_z, L.g_x, L.g_g, L.zx_bias,
+                                       L.zx_bias ? L.zx_bias + N : nullptr, L.gru, ob2, (long long)N, N, meta + h->off_whole_tok0, meta + h->off_whole_ntok,
+                                       meta + h->off_whole_slot, meta + h->off_whole_pos0));
+      TIMED(CLS_LINEAR, B200_TRY(linear<T>(h, ob2, (long long)N, L.r_o, mixo2, W, n_tok)));
+      y1 = mixo2; s0 = L.c.a_scale; s1 = L.c.b_scale;
+    } else {
+      const int C = 2 * L.Nq + L.Nv, Nd = a.heads * a.dim;
+      TIMED(CLS_ELEMENTWISE, B200_LAUNCH((causal_conv_kernel<T, float>), n_tok, 256, 0, st, proj, (long long)L.ldp, L.qkv_hist, L.qkv_conv, h->qkv32, (long long)C, C,
+                                         a.conv_taps, 0, tok_slot, tok_pos, tok_first);
+            if (a.conv_taps > 1) B200_LAUNCH(conv_carry_kernel<T>, n_tok, 256, 0, st, proj, (long long)L.ldp, L.qkv_hist, C, a.conv_taps - 1, tok_slot, tok_pos, tok_last));
+      // decay and gate pre-activations through their bottlenecks, fp32 out
+      TIMED(CLS_FOLD, B200_TRY(head_gemm(st, proj + L.c_a1, (long long)L.ldp, 0, static_cast<const T*>(L.a2), (long long)L.decay_rank, 0, h->gate32, (long long)Nd, 0,
+                                         n_tok, Nd, L.decay_rank, 1, 1.f, h->attn_tc != 0));
+            B200_TRY(head_gemm(st, proj + L.c_g1, (long long)L.ldp, 0, static_cast<const T*>(L.g2), (long long)L.gate_rank, 0, h->attn32, (long long)L.Nv, 0,
+                               n_tok, L.Nv, L.gate_rank, 1, 1.f, h->attn_tc != 0)));
+      ScanParams sp;
+      sp.proj = proj; sp.ld = L.ldp; sp.off_q = L.p_q; sp.off_k = L.p_k; sp.off_v = L.p_v; sp.z = nullptr; sp.zb = nullptr;
+      sp.inv_tau = 0.f; sp.cap = 0.f; sp.St = L.St; sp.nvec = nullptr; sp.mval = nullptr;
+      sp.out = h->scan32; sp.heads = a.heads; sp.dim = a.dim; sp.vdim = a.vdim;
+      sp.qscale = 1.f / sqrtf((float)a.dim);
+      const ScanLayout lay = scan_layout<MODE_CHDELTA>(h, sp, true);
+      TIMED(CLS_RECURRENT, B200_LAUNCH(chdelta_prep_kernel, n_tok, 256, (size_t)2 * a.kv_heads * sizeof(float), st, sp, h->qkv32, a.kv_heads, L.A_log, L.dt_bias, h->gate32,
+                                       h->small32 + L.s_ba, (long long)L.nsmall);
+            B200_TRY(check_launch("chdelta_prep"));
+            B200_TRY(scan_run<MODE_CHDELTA>(h, sp, lay, true)));
+      const long long rows = (long long)n_tok * a.heads;
+      TIMED(CLS_ELEMENTWISE, B200_LAUNCH((head_norm_gate_kernel<T, float>), (unsigned)ceil_div64(rows, 4), 128, 0, st, h->scan32, L.rnorm, 0, h->attn32, (long long)L.Nv, 0, 0, ob,
+                                         a.heads, a.vdim, rows, c.norm_eps));
+      TIMED(CLS_LINEAR, B200_TRY(linear<T>(h, ob, (long long)L.Nv, L.o, mixo, W, n_tok)));
+    }
+    const Layer* nx = last ? nullptr : &h->layers[li + 1];
+    float* trace = h->trace_layers ? h->trace + (long long)li * stride : nullptr;
+    if (mlp) {
+      TIMED(CLS_ELEMENTWISE, B200_TRY(streams_end<T>(h, mixo, s0, y1, s1, L.hc_mix[0], L.hc_out[0], nullptr, nullptr, L.hc_in[1], L.n2w, n_tok)));
+      T* act = static_cast<T*>(h->act);
+      T* upb = static_cast<T*>(h->act2);
+      TIMED(CLS_LINEAR, B200_TRY(linear<T>(h, hb, W, L.up, upb, L.c.ff, n_tok)));
+      const long long n = (long long)n_tok * L.c.ff;
+      TIMED(CLS_ELEMENTWISE, B200_LAUNCH(relu2_kernel<T>, (unsigned)ceil_div64(n, 256), 256, 0, st, upb, (long long)L.c.ff, 0, act, L.c.ff, n));
+      T* ffo = static_cast<T*>(h->ffo);
+      TIMED(CLS_LINEAR, B200_TRY(linear<T>(h, act, L.c.ff, L.down, ffo, W, n_tok)));
+      TIMED(CLS_ELEMENTWISE, B200_TRY(streams_end<T>(h, ffo, 1.f, (const T*)nullptr, 0.f, L.hc_mix[1], L.hc_out[1], trace, last ? h->xin : nullptr, nx ? nx->hc_in[0] : nullptr,
+                                                     nx ? nx->n1w : nullptr, n_tok)));
+    } else {
+      TIMED(CLS_ELEMENTWISE, B200_TRY(streams_end<T>(h, mixo, s0, y1, s1, L.hc_mix[0], L.hc_out[0], trace, last ? h->xin : nullptr, nx ? nx->hc_in[0] : nullptr,
+                                                     nx ? nx->n1w : nullptr, n_tok)));
+    }
+  }
+  B200_TRY(check_launch("decoder LM layers"));
+  if (n_want > 0) {
+    T* hf = static_cast<T*>(h->hf);
+    TIMED(CLS_ELEMENTWISE, B200_LAUNCH(rmsnorm_rows_kernel<T>, n_want, 256, 0, st, h->xin, meta + h->off_want, h->fnw, hf, W, c.norm_eps));
+    const long long n = (long long)n_want * c.vocab;
+    if (h->head.tiles) {
+      const int ldl = (c.vocab + 7) / 8 * 8;
+      TIMED(CLS_LINEAR, B200_TRY(linear<bf16>(h, reinterpret_cast<const bf16*>(hf), W, h->head, h->head_bf, ldl, n_want)));
+      B200_LAUNCH(scale_rows_kernel, (unsigned)ceil_div64(n, 256), 256, 0, st, h->head_bf, (long long)ldl, h->logits, c.vocab, n, c.logit_scale);
+    } else {
+      TIMED(CLS_LINEAR, B200_TRY(gemm_nt(st, hf, (long long)W, 0, static_cast<const T*>(h->head.rm), (long long)W, 0, h->logits, (long long)c.vocab, 0, n_want, c.vocab, W, 1, c.logit_scale)));
+    }
+    if (logits_out)
+      B200_CUDA(cudaMemcpyAsync(logits_out, h->logits, (size_t)n_want * c.vocab * 4, cudaMemcpyDeviceToDevice, st));
+  }
+  return check_launch("decoder LM step");
+}
+
 }  // namespace
 
 extern "C" {
@@ -1322,13 +1658,38 @@ int b200_dlm_create(const b200_dlm_config* cfg, b200_dlm** out) {
   if (!cfg || !out || !cfg->layers) B200_FAIL(B200_ERR_INVALID, "dlm_create: null argument");
   if (cfg->vocab < 1 || cfg->width < 1 || cfg->n_layers < 1) B200_FAIL(B200_ERR_INVALID, "dlm_create: vocab, width and n_layers must be positive");
   if (cfg->compute_dtype != B200_BF16 && cfg->compute_dtype != B200_F32) B200_FAIL(B200_ERR_INVALID, "dlm_create: compute_dtype must be bf16 or f32");
-  if (cfg->block != B200_BLOCK_GATED_DEPTH_AVERAGE && cfg->block != B200_BLOCK_SANDWICH && cfg->block != B200_BLOCK_PARALLEL_RESIDUAL)
+  if (cfg->block != B200_BLOCK_GATED_DEPTH_AVERAGE && cfg->block != B200_BLOCK_SANDWICH && cfg->block != B200_BLOCK_PARALLEL_RESIDUAL &&
+      cfg->block != B200_BLOCK_PRE_NORM_STREAMS)
     B200_FAIL(B200_ERR_INVALID, "dlm_create: unknown block arrangement %d", cfg->block);
+  if (cfg->block == B200_BLOCK_PRE_NORM_STREAMS && (cfg->streams < 0 || cfg->streams > B200_DLM_MAX_STREAMS))
+    B200_FAIL(B200_ERR_INVALID, "dlm_create: streams must be in 0..%d", B200_DLM_MAX_STREAMS);
+  if (cfg->tied_head && cfg->block != B200_BLOCK_PRE_NORM_STREAMS) B200_FAIL(B200_ERR_INVALID, "dlm_create: a tied head is registered for the pre-norm streams block only");
   if (cfg->canon_taps < 0 || cfg->canon_taps > 64) B200_FAIL(B200_ERR_INVALID, "dlm_create: canon_taps must be in 0..64");
   for (int i = 0; i < cfg->n_layers; ++i) {
     const b200_dlm_layer& l = cfg->layers[i];
     const b200_dlm_mixer &a = l.a, &b = l.b;
-    if (cfg->block == B200_BLOCK_PARALLEL_RESIDUAL) {
+    if (cfg->block == B200_BLOCK_PRE_NORM_STREAMS) {
+      if (a.heads < 1 || a.dim < 1 || a.vdim < 1) B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: heads, dim and vdim must be positive", i);
+      if (a.rot_dims < 0 || a.rot_dims % 2) B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: rot_dims must be even", i);
+      if (a.rot_dims > 0 && a.rot_scaling == B200_ROT_RAMP && (!(a.rot_factor > 0.f) || !(a.rot_original > 0.f) || !(a.rot_fast > 0.f) || !(a.rot_slow > 0.f) || !(a.rot_base > 1.f)))
+        B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: the rotary ramp wants positive factor, original, fast and slow", i);
+      if (a.window < 0) B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: the window must not be negative", i);
+      if (l.mixer == B200_MIXER_LATENT_ATTENTION) {
+        if (a.kv_rank < 1 || (a.kv_rank + a.rot_dims + 7) / 8 * 8 > 1024) B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: kv_rank + rot_dims in 1..1024", i);
+      } else if (l.mixer == B200_MIXER_PARALLEL) {
+        if (a.kind != B200_MIXER_WINDOW_ATTENTION || b.kind != B200_MIXER_MINGRU)
+          B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: a parallel pair of this block is window attention beside a minGRU", i);
+        if (a.kv_heads < 1 || a.heads % a.kv_heads || a.window < 1 || a.rot_dims > a.dim || a.conv_taps > 1)
+          B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: window attention wants heads a multiple of kv_heads, a positive window, rot_dims <= dim and no convolution", i);
+        if (b.dim < 1) B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: the minGRU wants a positive width", i);
+      } else if (l.mixer == B200_MIXER_CHANNEL_DELTA) {
+        if (a.dim > 256 || a.kv_heads < 1 || a.heads % a.kv_heads || a.conv_taps < 1 || a.conv_taps > 64)
+          B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: the delta rule wants dim in 1..256, heads a multiple of kv_heads and conv_taps in 1..64", i);
+      } else {
+        B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: mixer %d is not registered for this block arrangement", i, l.mixer);
+      }
+      if (l.mlp != B200_MLP_NONE && l.mlp != B200_MLP_DENSE_RELU2) B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: mlp kind %d is not registered for this block arrangement", i, l.mlp);
+    } else if (cfg->block == B200_BLOCK_PARALLEL_RESIDUAL) {
       if (a.heads < 1 || a.dim < 1 || a.vdim < 1) B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: heads, dim and vdim must be positive", i);
       if (a.rot_dims < 0 || a.rot_dims % 2 || a.rot_dims > a.dim) B200_FAIL(B200_ERR_INVALID, "dlm_create: layer %d: rot_dims must be even and at most dim", i);
       if (a.rot_dims > 0 && a.rot_scaling == B200_ROT_RAMP && (!(a.rot_factor > 0.f) || !(a.rot_original > 0.f) || !(a.rot_fast > 0.f) || !(a.rot_slow > 0.f) || !(a.rot_base > 1.f)))
@@ -1436,7 +1797,9 @@ int b200_dlm_finalize(b200_dlm* h) {
   };
   B200_TRY(matrix("embed", c.vocab, W, &h->embed));
   h->weight_bytes += (int64_t)c.vocab * W * es;
-  const bool sandwich = c.block == B200_BLOCK_SANDWICH, parallel = c.block == B200_BLOCK_PARALLEL_RESIDUAL;
+  const bool sandwich = c.block == B200_BLOCK_SANDWICH, parallel = c.block == B200_BLOCK_PARALLEL_RESIDUAL, streams = c.block == B200_BLOCK_PRE_NORM_STREAMS;
+  if (streams)
+    for (int i = 0; i < c.n_layers; ++i) B200_TRY(finalize_streams_layer(h, i, drop));
   if (sandwich) {
     B200_TRY(get_f32(h, "embed.norm", W, &h->embw));
     for (int i = 0; i < c.n_layers; ++i) B200_TRY(finalize_sandwich_layer(h, i, drop));
@@ -1445,7 +1808,7 @@ int b200_dlm_finalize(b200_dlm* h) {
     h->vmix_first = -1;
     for (int i = 0; i < c.n_layers; ++i) B200_TRY(finalize_parallel_layer(h, i, drop));
   }
-  for (int i = 0; i < c.n_layers && !sandwich && !parallel; ++i) {
+  for (int i = 0; i < c.n_layers && !sandwich && !parallel && !streams; ++i) {
     Layer& L = h->layers[i];
     const std::string p = "l" + std::to_string(i) + ".";
     const int64_t H = L.c.a.heads, dk = L.c.a.dim, dv = L.c.a.vdim, r = L.c.a.kv_rank, F = L.c.ff;
@@ -1499,10 +1862,18 @@ int b200_dlm_finalize(b200_dlm* h) {
   }
   B200_TRY(get_f32(h, "final.norm", W, &h->fnw));
   if (parallel) B200_LAUNCH(add_one_kernel, ceil_div((int)W, 256), 256, 0, nullptr, h->fnw, (int)W);      // stored around zero
-  if (!sandwich && !parallel) B200_TRY(get_f32(h, "final.norm.b", W, &h->fnb));
-  void* hd = nullptr;
-  B200_TRY(matrix("head", c.vocab, W, &hd));
-  B200_TRY(seal_weight(h, h->head, hd, c.vocab, (int)W, drop));
+  if (!sandwich && !parallel && !streams) B200_TRY(get_f32(h, "final.norm.b", W, &h->fnb));
+  if (c.tied_head) {      // the logits come from the embedding table: its rows stay (the gather), a packed copy serves the product
+    h->head.rm = h->embed; h->head.N = c.vocab; h->head.K = (int)W;
+    if (!h->f32 && h->use_tc && W % 8 == 0 && (c.vocab + 127) / 128 <= tc::SK_MAX_TILES) {
+      B200_TRY(h->weights.alloc(&h->head.tiles, tc::sk_packed_bytes(c.vocab, (int)W, 0, 0), false));
+      B200_TRY(tc::sk_pack_weights(static_cast<const bf16*>(h->embed), h->head.tiles, c.vocab, (int)W, 0, 0, nullptr));
+    }
+  } else {
+    void* hd = nullptr;
+    B200_TRY(matrix("head", c.vocab, W, &hd));
+    B200_TRY(seal_weight(h, h->head, hd, c.vocab, (int)W, drop));
+  }
   B200_CUDA(cudaDeviceSynchronize());
   for (void* p : drop) {
     auto it = std::find(h->weights.ptrs.begin(), h->weights.ptrs.end(), p);
@@ -1555,7 +1926,7 @@ int b200_dlm_cache_begin(b200_dlm* h, int slots, int capacity, int max_step_toke
   const size_t es = esize(h);
   const size_t T = (size_t)max_step_tokens, W = (size_t)c.width;
   h->stream = static_cast<cudaStream_t>(stream);
-  const bool sandwich = c.block == B200_BLOCK_SANDWICH, parallel = c.block == B200_BLOCK_PARALLEL_RESIDUAL;
+  const bool sandwich = c.block == B200_BLOCK_SANDWICH, parallel = c.block == B200_BLOCK_PARALLEL_RESIDUAL, streams = c.block == B200_BLOCK_PRE_NORM_STREAMS;
   size_t max_ldp = 0, max_hr = 0, max_hv = 0, max_ff = 1, max_r = 0, max_tiles = 0, max_qkv = 1, max_rv = 1, max_gate = 1, max_e = 1, max_top = 0, max_part = 0, max_prep = 4, max_segrow = 1, max_heads = 1;
   size_t max_small = 1, max_eff = 0, max_nv = 1;
   for (auto& L : h->layers) {
@@ -1563,6 +1934,32 @@ int b200_dlm_cache_begin(b200_dlm* h, int slots, int capacity, int max_step_toke
     max_ldp = std::max(max_ldp, (size_t)L.ldp);
     max_hv = std::max(max_hv, (size_t)a.heads * a.vdim);
     max_ff = std::max(max_ff, (size_t)L.c.ff);
+    if (streams) {
+      // per request: latents with the rotated key part; keys, values and the minGRU's vector; the matrix memory and the convolutions' last inputs
+      if (L.c.mixer == B200_MIXER_LATENT_ATTENTION) {
+        B200_TRY(A.alloc(&L.cache, (size_t)slots * capacity * L.rp * es));
+        max_hr = std::max(max_hr, (size_t)a.heads * L.rp);
+        max_r = std::max(max_r, (size_t)L.rp);
+      } else if (L.c.mixer == B200_MIXER_PARALLEL) {
+        B200_TRY(A.alloc(&L.kcache, (size_t)slots * capacity * L.Nk * es));
+        B200_TRY(A.alloc(&L.vcache, (size_t)slots * capacity * L.Nv * es));
+        B200_TRY(A.alloc_t(&L.gru, (size_t)slots * b.dim));
+        max_qkv = std::max(max_qkv, (size_t)L.Nq);
+        max_rv = std::max(max_rv, (size_t)b.dim);
+        max_part = std::max(max_part, (size_t)(L.sig_mma >= 0 ? 16 : L.QT) * a.heads * (a.vdim + 2));
+      } else {
+        const size_t C = (size_t)2 * L.Nq + L.Nv;
+        B200_TRY(A.alloc_t(&L.St, (size_t)slots * a.heads * a.vdim * a.dim));
+        if (a.conv_taps > 1) B200_TRY(A.alloc_t(&L.qkv_hist, (size_t)slots * (a.conv_taps - 1) * C));
+        max_qkv = std::max(max_qkv, C);
+        max_rv = std::max(max_rv, (size_t)a.heads * a.vdim);
+        max_gate = std::max(max_gate, (size_t)a.heads * a.dim);
+        max_prep = std::max(max_prep, (size_t)a.heads * (3 * (size_t)std::max(2 * a.dim, 64) + 4));
+        max_heads = std::max(max_heads, (size_t)a.heads);
+      }
+      max_small = std::max(max_small, (size_t)L.nsmall);
+      continue;
+    }
     if (parallel) {
       // per request: keys and values of an attention layer; the matrix memory of a recurrent one and its convolutions' last inputs
       if (L.c.mixer == B200_MIXER_SIGMOID_ATTENTION) {
@@ -1626,7 +2023,23 @@ int b200_dlm_cache_begin(b200_dlm* h, int slots, int capacity, int max_step_toke
     if (L.c.mlp == B200_MLP_MOE_RELU2) { max_e = std::max(max_e, (size_t)L.c.experts); max_top = std::max(max_top, (size_t)L.c.top); }
   }
   B200_TRY(A.alloc_t(&h->xin, T * W));
-  if (parallel) {
+  if (streams) {
+    B200_TRY(A.alloc_t(&h->xs, T * (size_t)std::max(c.streams, 1) * W));
+    B200_TRY(A.alloc_t(&h->qkv32, T * max_qkv));
+    B200_TRY(A.alloc_t(&h->small32, T * max_small));
+    B200_TRY(A.alloc_t(&h->scan32, T * max_rv));
+    B200_TRY(A.alloc_t(&h->scan_v, T * max_rv));
+    B200_TRY(A.alloc_t(&h->scan_prep, T * max_prep));
+    B200_TRY(A.alloc_t(&h->gate32, T * max_gate));
+    B200_TRY(A.alloc_t(&h->attn32, T * max_hv));
+    B200_TRY(A.alloc_t(&h->qa, T * std::max(max_hr, (size_t)1)));
+    B200_TRY(A.alloc_t(&h->ol, T * std::max(max_hr, (size_t)1)));
+    B200_TRY(A.alloc(&h->obuf2, T * max_rv * es));
+    B200_TRY(A.alloc(&h->mixo2, T * W * es));
+    B200_TRY(A.alloc(&h->ffo, T * W * es));
+    B200_TRY(A.alloc(&h->act2, T * max_ff * es));
+    h->part_floats = (size_t)600 * std::max(std::max(max_part, (size_t)16 * (max_r + 2)), (size_t)1);
+  } else if (parallel) {
     const size_t nseg = (size_t)(max_step_tokens / std::max(h->scan_seg, 8) + 2);
     B200_TRY(A.alloc_t(&h->qkv32, T * max_qkv));
     B200_TRY(A.alloc_t(&h->small32, T * max_small));
@@ -1844,7 +2257,8 @@ int b200_dlm_step(b200_dlm* h, int n_entries, const int32_t* slots_host, const i
   h->max_entry_tokens = 0;
   for (int e = 0; e < n_entries; ++e) h->max_entry_tokens = std::max(h->max_entry_tokens, (int)counts_host[e]);
   int rc;
-  if (h->cfg.block == B200_BLOCK_PARALLEL_RESIDUAL) rc = h->f32 ? step_parallel<float>(h, t, n_want, max_ctx, logits_dev) : step_parallel<bf16>(h, t, n_want, max_ctx, logits_dev);
+  if (h->cfg.block == B200_BLOCK_PRE_NORM_STREAMS) rc = h->f32 ? step_streams<float>(h, t, n_want, max_ctx, logits_dev) : step_streams<bf16>(h, t, n_want, max_ctx, logits_dev);
+  else if (h->cfg.block == B200_BLOCK_PARALLEL_RESIDUAL) rc = h->f32 ? step_parallel<float>(h, t, n_want, max_ctx, logits_dev) : step_parallel<bf16>(h, t, n_want, max_ctx, logits_dev);
   else if (h->cfg.block == B200_BLOCK_SANDWICH) rc = h->f32 ? step_sandwich<float>(h, t, n_want, max_ctx, logits_dev) : step_sandwich<bf16>(h, t, n_want, max_ctx, logits_dev);
   else rc = h->f32 ? step_body<float>(h, t, n_want, max_ctx, logits_dev) : step_body<bf16>(h, t, n_want, max_ctx, logits_dev);
   if (rc != B200_OK) return rc;

@@ -214,6 +214,11 @@ struct AttnParams {
   float* part;              // nsplit > 1: [tile][split][rows_per_tile][r + 2]
   int cap, r, H, nsplit;
   int* err = nullptr;       // device error flags (may be null)
+  // sink = null: an ordinary softmax.  window > 0: the row at position p sees keys j with 0 <= p - j < window.  gate != null:
+  // row (token, head) is multiplied by sigmoid(gate[token * ldg + head]).  (The tensor-core kernel takes none of the three.)
+  int window = 0;
+  const float* gate = nullptr;
+  int ldg = 0;
 };
 
 template <typename T, int NCH, int RPW>
@@ -227,9 +232,10 @@ __global__ void __launch_bounds__(128) latent_attn_kernel(AttnParams p) {
   const int row0 = p.tile_row0[tile], nrows = p.tile_rows[tile];
   const T* cbase = static_cast<const T*>(p.cache) + (long long)p.tile_slot[tile] * p.cap * r;
   const int kmax = p.tok_pos[(row0 + nrows - 1) / H];          // rows are ordered by token: the last row sees the most keys
-  const int n_kt = kmax / KT + 1;
+  const int kt_lo = p.window > 0 ? max(0, p.tok_pos[row0 / H] - p.window + 1) / KT : 0;      // the first row's window starts lowest
+  const int n_kt = kmax / KT + 1 - kt_lo;
   const int per = (n_kt + p.nsplit - 1) / p.nsplit;
-  const int kt0 = split * per, kt1 = min(n_kt, kt0 + per);
+  const int kt0 = kt_lo + split * per, kt1 = min(kt_lo + n_kt, kt0 + per);
 
   float q[RPW][NCH], o[RPW][NCH], m[RPW], lsum[RPW];
   int pos[RPW];
@@ -246,7 +252,7 @@ __global__ void __launch_bounds__(128) latent_attn_kernel(AttnParams p) {
       o[i][c] = 0.f;
     }
     // the sink enters once: the first split starts from (m = sink, l = 1); the others from nothing
-    if (split == 0 && valid) { m[i] = p.sink[g % H]; lsum[i] = lane == 0 ? 1.f : 0.f; }
+    if (split == 0 && valid && p.sink) { m[i] = p.sink[g % H]; lsum[i] = lane == 0 ? 1.f : 0.f; }
     else { m[i] = -INFINITY; lsum[i] = 0.f; }
   }
 
@@ -318,7 +324,7 @@ __global__ void __launch_bounds__(128) latent_attn_kernel(AttnParams p) {
     const int mykey = j0 + (lane & 3) * 8 + (lane >> 2);
 #pragma unroll
     for (int i = 0; i < RPW; ++i) {
-      const bool seen = mykey <= pos[i] && mykey <= kmax;
+      const bool seen = mykey <= pos[i] && mykey <= kmax && (p.window <= 0 || pos[i] - mykey < p.window);
       const float s = seen ? sc[i] : -INFINITY;
       const float mn = fmaxf(m[i], warp_max(s));
       float pj = 0.f;
@@ -357,7 +363,7 @@ __global__ void __launch_bounds__(128) latent_attn_kernel(AttnParams p) {
     if (lr >= nrows) continue;
     const float l = warp_sum(lsum[i]);
     if (p.nsplit == 1) {
-      const float inv = 1.f / l;
+      const float inv = (p.gate ? sigmoidf(p.gate[(long long)((row0 + lr) / H) * p.ldg + (row0 + lr) % H]) : 1.f) / l;
       float* dst = p.out + (long long)(row0 + lr) * r;
 #pragma unroll
       for (int c = 0; c < NCH; ++c) { const int e = lane + 32 * c; if (e < r) dst[e] = o[i][c] * inv; }
@@ -599,7 +605,8 @@ __global__ void __launch_bounds__(128, 3) latent_attn_mma_kernel(AttnParams p) {
 // sums them over the splits with independent 8-byte loads (scalar loads when the latent size is odd).
 __global__ void __launch_bounds__(128) latent_attn_merge_kernel(const float* __restrict__ part, const int* __restrict__ tile_row0,
                                                                 const int* __restrict__ tile_rows, float* __restrict__ out, int r,
-                                                                int nsplit, int rows_per_tile) {
+                                                                int nsplit, int rows_per_tile, const float* __restrict__ gate = nullptr,
+                                                                int ldg = 0, int H = 1) {      // gate: row (token, head) times sigmoid(gate[token * ldg + head])
   __shared__ float wsm[64];
   const int tile = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int lr = blockIdx.y;
@@ -620,7 +627,8 @@ __global__ void __launch_bounds__(128) latent_attn_merge_kernel(const float* __r
     w[i] = ms[i] > -INFINITY ? expf(ms[i] - M) : 0.f;
     L += ls[i] * w[i];
   }
-  const float inv = 1.f / warp_sum(L);
+  float inv = 1.f / warp_sum(L);
+  if (gate) { const int row = tile_row0[tile] + lr; inv *= sigmoidf(gate[(long long)(row / H) * ldg + row % H]); }
   if (warp == 0) { wsm[lane] = w[0]; wsm[lane + 32] = w[1]; }
   __syncthreads();
   float* dst = out + (long long)(tile_row0[tile] + lr) * r;

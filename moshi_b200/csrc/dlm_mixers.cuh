@@ -553,7 +553,8 @@ __global__ void __launch_bounds__(256) small_proj_f32_kernel(const T* __restrict
 // ---------------------------------------------------------------------------------------------------------------------------
 //   MODE_DELTA (the gated delta rule): S <- g_t S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t
 //       (g, beta per head and token; a column of S depends on no other column, so the columns are dealt over threads as above)
-enum { MODE_DECAY = 0, MODE_EXPGATE = 1, MODE_DELTA = 2 };
+//   MODE_CHDELTA: the same with one decay per key channel, S <- diag(g_t) S (prep row [q | k | g | beta])
+enum { MODE_DECAY = 0, MODE_EXPGATE = 1, MODE_DELTA = 2, MODE_CHDELTA = 3 };
 
 struct ScanParams {
   const void* proj;         // T [tokens][ld]: q at off_q, k at off_k, v at off_v (heads x dim / vdim each)
@@ -749,8 +750,8 @@ __global__ void __launch_bounds__(128) matrix_memory_scan_kernel(ScanParams p) {
         m = m2;
         logF += fl;
       }
-      if (MODE == MODE_DELTA) {      // two passes over the thread's rows: decay and S^T k, then the write and the read-out
-        const float gl = aa[0], be = aa[1];
+      if (MODE == MODE_DELTA || MODE == MODE_CHDELTA) {      // two passes over the thread's rows: decay and S^T k, then the write and the read-out
+        const float gl = aa[0], be = MODE == MODE_CHDELTA ? aa[VL ? Dp : dim] : aa[1];
         float dot[CB], u[CB];
 #pragma unroll
         for (int j = 0; j < CB; ++j) dot[j] = 0.f;
@@ -758,8 +759,9 @@ __global__ void __launch_bounds__(128) matrix_memory_scan_kernel(ScanParams p) {
         for (int i = 0; i < R; ++i) {
           const int r = VL ? rg * R + i : rg + LPC * i;
           const float kv = VL ? kk[((i >> 2) * LPC + rg) * 4 + (i & 3)] : (r < dim ? kk[r] : 0.f);
+          const float gr = MODE == MODE_CHDELTA ? (VL ? aa[((i >> 2) * LPC + rg) * 4 + (i & 3)] : (r < dim ? aa[r] : 0.f)) : gl;      // the row's own decay
 #pragma unroll
-          for (int j = 0; j < CB; ++j) { S[i][j] *= gl; dot[j] = fmaf(S[i][j], kv, dot[j]); }
+          for (int j = 0; j < CB; ++j) { S[i][j] *= gr; dot[j] = fmaf(S[i][j], kv, dot[j]); }
         }
 #pragma unroll
         for (int j = 0; j < CB; ++j) {
@@ -942,9 +944,9 @@ __global__ void __launch_bounds__(128) mlstm_combine_kernel(float* __restrict__ 
 
 // what leaves a recurrent mixer: per head rms_norm over vdim (weight w[h * wstride + c]: wstride = 0 shares one row between
 // the heads, w = null: no weight), times a gate computed from the projection g (act 0: sigmoid, 1: silu) -> T.  One warp per (token, head).
-template <typename T>
+template <typename T, typename TG = T>      // TG: type of the gate's pre-activations (fp32 when they come from a product of their own)
 __global__ void __launch_bounds__(128) head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ w, int wstride,
-                                                             const T* __restrict__ proj, long long ld, int off_g, int act, T* __restrict__ out,
+                                                             const TG* __restrict__ proj, long long ld, int off_g, int act, T* __restrict__ out,
                                                              int heads, int vdim, long long rows, float eps) {
   const long long row = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
   if (row >= rows) return;

@@ -83,26 +83,28 @@ __device__ __forceinline__ void rotary_fill(float* rot, int half, int pos, const
 
 // element d of a head after rotation; `head` points at the head's first element
 template <typename T>
-__device__ __forceinline__ float rotary_at(const T* __restrict__ head, int d, int half, int adjacent, const float* __restrict__ rot) {
-  const float own = to_f(head[d]);
+__device__ __forceinline__ float rotary_at(const T* __restrict__ head, int d, int half, int adjacent, const float* __restrict__ rot,
+                                           const float* __restrict__ hb = nullptr) {      // hb: the head's bias, added before the rotation
+  const float own = to_f(head[d]) + (hb ? hb[d] : 0.f);
   if (d >= 2 * half) return own;
   int i, partner; bool first;
   if (adjacent) { i = d >> 1; first = (d & 1) == 0; partner = d ^ 1; }
   else { first = d < half; i = first ? d : d - half; partner = first ? d + half : d - half; }
-  const float other = to_f(head[partner]);
+  const float other = to_f(head[partner]) + (hb ? hb[partner] : 0.f);
   return first ? own * rot[i] - other * rot[half + i] : own * rot[i] + other * rot[half + i];
 }
 
 // Query / key / value preparation of the sigmoid attention, one CTA per token, on the projections proj T [tokens][ld]:
 //   q <- rope(q) * qscale -> qout fp32 [tokens][Nq];   k <- rope(k) -> key cache row;
 //   v <- (1 - lambda) v + lambda v_first (when v_first is given) -> value cache row;   v -> v_keep (when given: this layer's
-//   values are what later layers blend in).
+//   values are what later layers blend in).  Also the preparation of a window attention without norms or convolution.
 template <typename T>
 __global__ void __launch_bounds__(256) attn_rope_cache_kernel(const T* __restrict__ proj, long long ld, int off_q, int off_k, int off_v, int Nq, int Nk,
                                                               int Nv, int dim, int half, int adjacent, const double* __restrict__ freq, float amp,
                                                               float qscale, float* __restrict__ qout, T* __restrict__ kcache, T* __restrict__ vcache,
                                                               int cap, const int* __restrict__ tok_slot, const int* __restrict__ tok_pos,
-                                                              const T* __restrict__ v_first, const float* __restrict__ lambda, T* __restrict__ v_keep) {
+                                                              const T* __restrict__ v_first, const float* __restrict__ lambda, T* __restrict__ v_keep,
+                                                              const float* __restrict__ bias = nullptr) {      // bias: fp32 [Nq | Nk | Nv], added to the projections
   extern __shared__ float rot[];        // [half] cosines, [half] sines
   const long long t = blockIdx.x;
   const T* row = proj + t * ld;
@@ -112,17 +114,18 @@ __global__ void __launch_bounds__(256) attn_rope_cache_kernel(const T* __restric
   __syncthreads();
   for (int e = threadIdx.x; e < Nq; e += blockDim.x) {
     const int hh = e / dim, d = e - hh * dim;
-    qout[t * Nq + e] = rotary_at(row + off_q + hh * dim, d, half, adjacent, rot) * qscale;
+    qout[t * Nq + e] = rotary_at(row + off_q + hh * dim, d, half, adjacent, rot, bias ? bias + hh * dim : nullptr) * qscale;
   }
   T* kc = kcache + crow * Nk;
   for (int e = threadIdx.x; e < Nk; e += blockDim.x) {
     const int hh = e / dim, d = e - hh * dim;
-    kc[e] = from_f<T>(rotary_at(row + off_k + hh * dim, d, half, adjacent, rot));
+    kc[e] = from_f<T>(rotary_at(row + off_k + hh * dim, d, half, adjacent, rot, bias ? bias + Nq + hh * dim : nullptr));
   }
   T* vc = vcache + crow * Nv;
   const float lam = v_first ? lambda[0] : 0.f;
   for (int e = threadIdx.x; e < Nv; e += blockDim.x) {
-    const T raw = row[off_v + e];
+    T raw = row[off_v + e];
+    if (bias) raw = from_f<T>(to_f(raw) + bias[Nq + Nk + e]);
     if (v_keep) v_keep[t * Nv + e] = raw;
     vc[e] = v_first ? from_f<T>((1.f - lam) * to_f(raw) + lam * to_f(v_first[t * Nv + e])) : raw;
   }

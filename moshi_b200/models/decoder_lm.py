@@ -12,7 +12,7 @@ import typing as tp
 import torch
 
 from .. import _lib
-from ..config import BLOCKS, MIXERS, MLP_KINDS, ROT_PAIRINGS, ROT_SCALINGS, DecoderLMConfig, MixerConfig
+from ..config import BLOCKS, MIXERS, MLP_KINDS, ROT_PAIRINGS, ROT_SCALINGS, SINKS, DecoderLMConfig, MixerConfig
 
 _DTYPES = {torch.bfloat16: _lib.B200_BF16, torch.float32: _lib.B200_F32}
 
@@ -27,6 +27,7 @@ def _fill_mixer(dst, m: MixerConfig) -> None:
     dst.rot_scaling = ROT_SCALINGS[m.rot_scaling_kind if m.rot_scaling else None] if m.rot_scaling_kind else (1 if m.rot_scaling else 0)
     dst.rot_fast, dst.rot_slow = float(sc.get("fast", 0.0)), float(sc.get("slow", 0.0))
     dst.softcap, dst.v_mix = m.softcap, int(m.v_mix)
+    dst.bias, dst.sink, dst.head_gate = int(m.bias), SINKS[m.sink], int(m.head_gate)
     if m.decay:
         dst.decay = (C.c_float * len(m.decay))(*m.decay)      # ctypes keeps the array alive with the struct; create() copies it
 
@@ -53,6 +54,7 @@ class DecoderLM:
             layers[i].mixer, layers[i].mlp, layers[i].ff = MIXERS[L.type], MLP_KINDS[L.mlp_kind], L.ff
             layers[i].experts, layers[i].top = L.experts, L.top
             layers[i].expert_limit, layers[i].router_scale = L.expert_limit, L.router_scale
+            layers[i].a_scale, layers[i].b_scale = L.a_scale, L.b_scale
             for dst, m in zip((layers[i].a, layers[i].b), L.mixers()):
                 if m is not None:
                     _fill_mixer(dst, m)
@@ -60,6 +62,7 @@ class DecoderLM:
         c.vocab, c.width, c.n_layers = cfg.vocab, cfg.width, len(cfg.layers)
         c.embedding_scale, c.residual_mult, c.norm_eps = cfg.embedding_scale, cfg.residual_mult, cfg.norm_eps
         c.block, c.canon_taps, c.logit_softcap = BLOCKS[cfg.block], cfg.canon_taps, cfg.logit_softcap
+        c.streams, c.logit_scale, c.tied_head = cfg.streams, cfg.logit_scale, int(cfg.tied_head)
         c.compute_dtype = _DTYPES[dtype]
         c.layers = layers
         items = tensors.items() if isinstance(tensors, tp.Mapping) else tensors

@@ -281,6 +281,12 @@ def iter_synth_decoder_tensors(cfg: DecoderLMConfig, seed: int = 99, device="cpu
         last = leaf.rsplit(".", 1)[-1]
         if zero_centred and leaf in ("norm1", "final.norm"):
             t = _uniform(gen, shape, 0.2, device)
+        elif leaf.startswith("hc") and last == "in":          # residual streams: read weights sum to about one,
+            t = 1.0 / shape[0] + _uniform(gen, shape, 0.3 / shape[0], device)
+        elif leaf.startswith("hc") and last == "out":         # every stream takes the sublayer's result about once,
+            t = 1.0 + _uniform(gen, shape, 0.2, device)
+        elif leaf.startswith("hc") and last == "mix":         # and the streams mostly keep themselves
+            t = torch.eye(shape[0], device=device) + _uniform(gen, shape, 0.3 / shape[0], device)
         elif last == "vmix":            # how much of the first blending layer's values a later one takes
             t = 0.3 + _uniform(gen, shape, 0.2, device)
         elif last == "pb":              # sigmoid weights are not normalised over keys: start them small
