@@ -296,12 +296,19 @@ class Oracle:
             tr.append(torch.stack(b))
         return torch.stack(lg), torch.stack(tr, 1)
 
+    def forward(self, tokens, return_layers=False):
+        lg, tr = self.run(tokens)
+        return (lg, tr) if return_layers else lg
+
     def greedy(self, prompt, n_new):
+        """(tokens, gap between the two largest logits at every choice)."""
         st = self.new_state()
         lg, _ = self.run(prompt, st)
-        out = []
+        out, gaps = [], []
         for _ in range(n_new):
+            top = lg[-1].topk(2).values
             nxt = int(lg[-1].argmax())
             out.append(nxt)
+            gaps.append(float(top[0] - top[1]))
             lg, _ = self.run([nxt], st)
-        return out
+        return out, gaps
