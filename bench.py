@@ -898,6 +898,161 @@ def namalix_arm(args) -> None:
     print(json.dumps(out))
 
 
+# ---------------------------------------------------------------------------------------------
+# --decoder-lm --decoder-arch dibulix: the Dibulix design, whole and one mixer kind at a time, beside the like kernels of the
+# existing designs at equal shapes (Likosun: latent attention; Govuvik: window attention beside a recurrence; Namalix: delta
+# rule; and a Namalix model of equal width, depth, head shapes and vocabulary as the closest whole model)
+# ---------------------------------------------------------------------------------------------
+DIBULIX_SIZES = {
+    # name: (width, layer kinds, attention heads, kv heads, head dim, rotated dims, kv_rank, window, recurrent heads, key dim, value dim, minGRU width, ff, vocab, streams)
+    "w2048": (2048, ("channel_delta", "latent_attention", "parallel", "channel_delta"), 16, 4, 128, 64, 512, 1024, 8, 128, 256, 4096, 8192, 32000, 4),
+    "w4096": (4096, ("channel_delta", "latent_attention", "parallel"), 16, 4, 128, 64, 512, 1024, 16, 128, 256, 8192, 16384, 32000, 4),
+}
+
+
+def _dibulix_cfgs(size: str) -> dict:
+    """name -> configuration: the whole model, two-layer models of one mixer kind each, and the comparators."""
+    from moshi_b200.config import DecoderLMConfig
+    W, kinds, H, G, d, rd, r, win, Hr, dk, dv, N, ff, V, S = DIBULIX_SIZES[size]
+    ramp = {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}
+    mix = {
+        "latent_attention": {"dim": d, "heads": H, "kv_rank": r, "mask": {"size": win}, "rot_dim": rd, "rot": {"base": 1e6, "dims": rd, "scaling": ramp},
+                             "scale": (d + rd) ** -0.5, "vdim": d},
+        "parallel": {"left": {"dim": d, "heads": H, "kv_heads": G, "mask": {"size": win}, "rot": {"base": 5e5, "dims": d // 2}, "scale": d ** -0.5, "vdim": d},
+                     "left_scale": 1.2, "right": {"width": N}, "right_scale": 1.1},
+        "channel_delta": {"conv": 4, "dim": dk, "heads": Hr, "kv_heads": Hr, "vdim": dv},
+    }
+    dense = {"ff": ff, "kind": "dense"}
+
+    def dib(layer_kinds, mlps):
+        cfg = DecoderLMConfig.from_dict({"architecture": "Dibulix", "logit_scale": 0.25, "norm": {"eps": 1e-6}, "streams": S, "vocab": V, "width": W,
+                                         "layers": [{"type": k, "mixer": mix[k], "mlp": m} for k, m in zip(layer_kinds, mlps)]})
+        for L in cfg.layers:
+            if L.type == "channel_delta":
+                L.a.decay_rank = L.a.gate_rank = 64
+        return cfg
+    n = len(kinds)
+    out = {"dibulix": dib(kinds, [None if k == "channel_delta" else dense for k in kinds])}
+    for k in ("latent_attention", "parallel", "channel_delta"):
+        out["dibulix/" + k] = dib((k, k), (None, None))
+    out["likosun/latent_attention"] = DecoderLMConfig.from_dict({
+        "architecture": "Likosun", "vocab": V, "width": W, "embedding": {"scale": 1.0}, "residual_mult": 0.5, "norm": {"eps": 1e-6},
+        "layers": [{"type": "latent_attention", "mixer": {"heads": H, "dim": d, "vdim": d, "kv_rank": r, "scale": d ** -0.5}, "mlp": None}] * 2})
+    left = {"conv": 0, "dim": d, "heads": H, "kv_heads": G, "mask": {"size": win}, "rot": {"base": 5e5, "dims": d // 2}, "scale": d ** -0.5, "vdim": d}
+    out["govuvik/parallel"] = DecoderLMConfig.from_dict({
+        "architecture": "Govuvik", "canon": {"taps": 0}, "logit_softcap": 30.0, "norm": {"eps": 1e-6}, "vocab": V, "width": W,
+        "layers": [{"type": "parallel", "mixer": {"left": left, "right": {"dim": dk, "heads": Hr, "tau": 8.0, "vdim": dv}}, "mlp": None}] * 2})
+    nam_delta = {"type": "delta", "mixer": {"conv": 4, "dim": dk, "heads": Hr, "kv_heads": Hr, "vdim": dv}}
+    nam_attn = {"type": "attention", "mixer": {"dim": d, "heads": H, "kv_heads": G, "scale": d ** -0.5, "softcap": 50.0, "v_mix": False, "vdim": d,
+                                               "rot": {"base": 5e5, "dims": d // 2}}}
+    nam = lambda layers: DecoderLMConfig.from_dict({"architecture": "Namalix", "embedding": {"scale": W ** 0.5}, "norm": {"eps": 1e-6}, "vocab": V, "width": W, "layers": layers})
+    out["namalix/delta"] = nam([dict(nam_delta, mlp=None)] * 2)
+    # the closest whole model: delta rule where this design has it, attention elsewhere, a dense (gated) feed-forward of the same
+    # three-matrix cost 2/3 ff where this design has its two-matrix one
+    out["namalix_equal"] = nam([dict(nam_delta if k == "channel_delta" else nam_attn, mlp=None if k == "channel_delta" else {"ff": ff * 2 // 3 // 64 * 64, "kind": "dense"})
+                                for k in kinds])
+    return out
+
+
+def dibulix_arm(args) -> None:
+    """Prefill (one prompt of --prefill-tokens) and decode (--decode-batch requests, one token each, on --context cached tokens)
+    of the Dibulix design with random weights, per size: whole steps, and per class of kernel for two-layer models of one mixer
+    kind, each beside the like kernel of the existing design that has it, against the measured rooflines."""
+    from moshi_b200 import _lib
+    from moshi_b200.models import DecoderLMGen, loaders
+    device = torch.device("cuda:0")
+    torch.cuda.set_device(device)
+    hbm, src = _peaks()
+    pk = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+    tf = float(pk.get("bf16_tflops", 1590.0))
+    T, B, ctx = args.prefill_tokens, args.decode_batch, args.context
+    g = torch.Generator().manual_seed(7)
+    out = {"impl": "b200", "mode": "decoder-lm", "arch": "dibulix", "dtype": "bf16", "data": "synthetic (random weights)",
+           "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "source": src}, "workload": {"prefill_tokens": T, "decode_batch": B, "context": ctx}, "sizes": {}}
+    launches0 = _lib.lib().b200_launch_count()
+
+    def measure(cfg):
+        model = loaders.get_decoder_lm(None, cfg, device=device, synth_seed=11)
+        gen = DecoderLMGen(model, slots=B, capacity=ctx + 64, max_step_tokens=max(T, B), max_want=B)
+        V = cfg.vocab
+        prompt = torch.randint(0, V, (T,), generator=g).tolist()
+
+        def prefill():
+            gen.step([(0, prompt)], [T - 1])
+            gen.release(0)
+
+        def classes(fn):
+            gen.set_option("time_kernels", 1)
+            gen.kernel_times()
+            for _ in range(3):
+                fn()
+            kt = {k: v / 3 for k, v in gen.kernel_times().items()}
+            gen.set_option("time_kernels", 0)
+            return kt
+        res = {"prefill": {"ms": _timed_steps(prefill, args.steps, args.warmup)}}
+        res["prefill"]["tokens_per_s"] = T / res["prefill"]["ms"] * 1e3
+        res["prefill"]["kernel_ms"] = classes(prefill)
+        res["prefill"]["tflops"] = model.algorithmic_flops(T, 0) / res["prefill"]["ms"] / 1e9
+        filler = torch.randint(0, V, (ctx,), generator=g).tolist()
+        for b in range(B):
+            for a in range(0, ctx, max(T, B)):
+                gen.step([(b, filler[a:a + max(T, B)])], [])
+        toks = torch.randint(0, V, (B,), generator=g).tolist()
+
+        def decode():
+            gen.step([(b, [toks[b]]) for b in range(B)], list(range(B)))
+        res["decode"] = {"ms": _timed_steps(decode, min(args.steps, 40), min(args.warmup, 5))}
+        res["decode"]["tokens_per_s"] = B / res["decode"]["ms"] * 1e3
+        res["decode"]["kernel_ms"] = classes(decode)
+        nbytes = model.algorithmic_bytes(B, B * ctx)
+        res["decode"].update({"algorithmic_bytes": nbytes, "frac_of_hbm_peak": nbytes / res["decode"]["ms"] / 1e6 / hbm})
+        assert gen.error_flags() == 0
+        gen.close()
+        del gen, model
+        torch.cuda.empty_cache()
+        return res
+
+    for size in args.decoder_sizes.split(","):
+        W, kinds, H, G, d, rd, r, win, Hr, dk, dv, N, ff, V, S = DIBULIX_SIZES[size]
+        res = {"config": dict(zip(("width", "layers", "heads", "kv_heads", "head_dim", "rot_dim", "kv_rank", "window", "recurrent_heads", "key_dim", "value_dim",
+                                   "mingru_width", "ff", "vocab", "streams"), DIBULIX_SIZES[size])), "models": {}}
+        for name, cfg in _dibulix_cfgs(size).items():
+            res["models"][name] = measure(cfg)
+        m = res["models"]
+        # (query, key) pairs of a prompt of T tokens: inside a window, and causal
+        pw = sum(min(t + 1, win) for t in range(T))
+        pc = T * (T + 1) // 2
+        seen = min(ctx + 1, win)
+        rp = (r + rd + 63) // 64 * 64
+
+        def per_layer(name, phase, cls):
+            return m[name][phase]["kernel_ms"][cls] / 2
+        # fractions of the measured peaks of one layer's kernels: tensor-core FLOPs in prefill, cache or state bytes in decode
+        res["like_kernels"] = {
+            "latent_attention": {
+                "prefill_frac_of_bf16_peak": {"dibulix": 4 * pw * H * (r + rd) / per_layer("dibulix/latent_attention", "prefill", "attention") / 1e9 / tf,
+                                              "likosun": 4 * pc * H * r / per_layer("likosun/latent_attention", "prefill", "attention") / 1e9 / tf},
+                "decode_frac_of_hbm_peak": {"dibulix": B * seen * rp * 2 / per_layer("dibulix/latent_attention", "decode", "attention") / 1e6 / hbm,
+                                            "likosun": B * (ctx + 1) * r * 2 / per_layer("likosun/latent_attention", "decode", "attention") / 1e6 / hbm}},
+            "window_attention": {
+                "prefill_frac_of_bf16_peak": {"dibulix": 4 * pw * H * d / per_layer("dibulix/parallel", "prefill", "attention") / 1e9 / tf,
+                                              "govuvik": 4 * pw * H * d / per_layer("govuvik/parallel", "prefill", "attention") / 1e9 / tf},
+                "decode_frac_of_hbm_peak": {"dibulix": B * seen * 2 * G * d * 2 / per_layer("dibulix/parallel", "decode", "attention") / 1e6 / hbm,
+                                            "govuvik": B * seen * 2 * G * d * 2 / per_layer("govuvik/parallel", "decode", "attention") / 1e6 / hbm}},
+            "delta_rule": {
+                "prefill_ms_per_layer": {"dibulix": per_layer("dibulix/channel_delta", "prefill", "recurrent"), "namalix": per_layer("namalix/delta", "prefill", "recurrent")},
+                "decode_frac_of_hbm_peak": {"dibulix": 2 * B * Hr * dk * dv * 4 / per_layer("dibulix/channel_delta", "decode", "recurrent") / 1e6 / hbm,
+                                            "namalix": 2 * B * Hr * dk * dv * 4 / per_layer("namalix/delta", "decode", "recurrent") / 1e6 / hbm}},
+            "vector_recurrence_beside_attention": {
+                "prefill_frac_of_hbm_peak": {"dibulix_mingru": T * N * 8 / per_layer("dibulix/parallel", "prefill", "recurrent") / 1e6 / hbm},
+                "prefill_ms_per_layer": {"dibulix_mingru": per_layer("dibulix/parallel", "prefill", "recurrent"), "govuvik_gla": per_layer("govuvik/parallel", "prefill", "recurrent")},
+                "decode_ms_per_layer": {"dibulix_mingru": per_layer("dibulix/parallel", "decode", "recurrent"), "govuvik_gla": per_layer("govuvik/parallel", "decode", "recurrent")}},
+        }
+        out["sizes"][size] = res
+    out["gpu_launches"] = int(_lib.lib().b200_launch_count() - launches0)
+    print(json.dumps(out))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -915,16 +1070,17 @@ def main() -> None:
     ap.add_argument("--decoder-lm", action="store_true",
                     help="instead of the default workload: prefill / decode throughput of the text-only decoder LM (Likosun design, random "
                          "weights) beside the Moshi temporal transformer at equal width and depth; prints its own JSON line")
-    ap.add_argument("--decoder-arch", choices=["likosun", "govuvik", "namalix"], default="likosun",
+    ap.add_argument("--decoder-arch", choices=["likosun", "govuvik", "namalix", "dibulix"], default="likosun",
                     help="with --decoder-lm: which design to time (govuvik: window attention beside gated linear attention, mLSTM, routed experts; "
-                         "namalix: sigmoid attention, retention, delta rule, clamped routed experts)")
+                         "namalix: sigmoid attention, retention, delta rule, clamped routed experts; dibulix: residual streams, latent attention "
+                         "with a rotated key part, window attention beside a minGRU, delta rule with a decay per key channel)")
     ap.add_argument("--decoder-sizes", default="w2048,w4096", help="comma-separated names out of " + ",".join(DECODER_SIZES))
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--decode-batch", type=int, default=32)
     ap.add_argument("--context", type=int, default=2048)
     args = ap.parse_args()
     if args.decoder_lm:
-        {"govuvik": govuvik_arm, "namalix": namalix_arm}.get(args.decoder_arch, decoder_lm_arm)(args)
+        {"govuvik": govuvik_arm, "namalix": namalix_arm, "dibulix": dibulix_arm}.get(args.decoder_arch, decoder_lm_arm)(args)
         return
     if args.impl == "reference":
         reference_arm(args)

@@ -141,7 +141,7 @@ struct b200_dlm {
 namespace {
 
 size_t esize(const b200_dlm* h) { return h->f32 ? 4 : 2; }
-int rows_per_tile(int r) { return r <= 512 ? 16 : 8; }
+int rows_per_tile(int r) { return r <= 576 ? 16 : 8; }
 
 template <typename TO>
 int convert_into(const Tensor* t, TO* dst) {
@@ -279,8 +279,8 @@ int launch_attn_mma(cudaStream_t st, const AttnParams& p, int tiles) {
   return check_launch("latent_attn_mma");
 }
 
-// bf16 latents of 64, 128, .., 512 elements take the tensor-core kernel
-inline bool attn_mma_takes(int r, int rpt, bool bf16_latents) { return bf16_latents && rpt == 16 && r % 64 == 0 && r <= 512; }
+// bf16 rows of 64, 128, .., 576 elements (512 of latent + 64 of a rotated key part) take the tensor-core kernel
+inline bool attn_mma_takes(int r, int rpt, bool bf16_latents) { return bf16_latents && rpt == 16 && r % 64 == 0 && r <= 576; }
 
 template <typename T>
 int run_attention(cudaStream_t st, AttnParams p, int tiles, int rpt, bool tensor_cores = true) {
@@ -294,13 +294,15 @@ int run_attention(cudaStream_t st, AttnParams p, int tiles, int rpt, bool tensor
       case 5: B200_TRY(launch_attn_mma<5>(st, p, tiles)); break;
       case 6: B200_TRY(launch_attn_mma<6>(st, p, tiles)); break;
       case 7: B200_TRY(launch_attn_mma<7>(st, p, tiles)); break;
-      default: B200_TRY(launch_attn_mma<8>(st, p, tiles)); break;
+      case 8: B200_TRY(launch_attn_mma<8>(st, p, tiles)); break;
+      default: B200_TRY(launch_attn_mma<9>(st, p, tiles)); break;
     }
   }
   else if (r <= 64) B200_TRY((launch_attn<T, 2, 4>(st, p, tiles, p.nsplit)));
   else if (r <= 128) B200_TRY((launch_attn<T, 4, 4>(st, p, tiles, p.nsplit)));
   else if (r <= 256) B200_TRY((launch_attn<T, 8, 4>(st, p, tiles, p.nsplit)));
   else if (r <= 512) B200_TRY((launch_attn<T, 16, 4>(st, p, tiles, p.nsplit)));
+  else if (r <= 576) B200_TRY((launch_attn<T, 18, 4>(st, p, tiles, p.nsplit)));
   else B200_TRY((launch_attn<T, 32, 2>(st, p, tiles, p.nsplit)));
   if (p.nsplit > 1) {
     B200_LAUNCH(latent_attn_merge_kernel, dim3(tiles, rpt), 128, 0, st, p.part, p.tile_row0, p.tile_rows, p.out, r, p.nsplit, rpt, p.gate, p.ldg, p.H);
@@ -1381,6 +1383,10 @@ int finalize_streams_layer(b200_dlm* h, int i, std::vector<void*>& drop) {
     L.off_q = 0; L.off_dkv = pad8(L.Nq); L.ncat = L.off_dkv + (int)(r + rd);
     L.ldp = pad8(L.ncat);
     L.rp = pad8((int)(r + rd));
+    {   // bf16: rows padded to a multiple of 64 take the tensor-core kernel, when that costs at most a third more cache
+      const int rp64 = (int)(r + rd + 63) / 64 * 64;
+      if (!h->f32 && h->use_tc && rp64 <= 576 && (int64_t)rp64 * 3 <= (r + rd) * 4) L.rp = rp64;
+    }
     B200_TRY(h->weights.alloc(&cat, (size_t)L.ncat * W * es, true));
     B200_TRY(put_matrix(h, m + "q", H * dq, W, at(L.off_q)));
     B200_TRY(put_matrix(h, m + "dkv", r + rd, W, at(L.off_dkv)));
@@ -1541,7 +1547,7 @@ int latent_rope_attention(b200_dlm* h, const Layer& L, int n_tok, int max_ctx) {
   if (a.head_gate) { p.gate = h->small32 + L.s_gate; p.ldg = L.nsmall; }
   const int seen = a.window > 0 ? std::min(max_ctx, a.window + 32) : max_ctx;
   p.nsplit = pick_split(h->attn_split, s.count, seen, s.rpt, rp, h->part_floats);
-  TIMED(CLS_ATTN, B200_TRY(run_attention<T>(st, p, s.count, s.rpt, false)));
+  TIMED(CLS_ATTN, B200_TRY(run_attention<T>(st, p, s.count, s.rpt, h->attn_tc != 0)));
   T* ob = static_cast<T*>(h->obuf);
   TIMED(CLS_FOLD, B200_TRY(head_gemm(st, h->ol, (long long)H * rp, (long long)rp, static_cast<const T*>(L.uv), (long long)r, (long long)dv * r, ob, (long long)H * dv,
                                      (long long)dv, n_tok, dv, r, H, 1.f, h->attn_tc != 0)));
@@ -1584,7 +1590,8 @@ int step_streams(b200_dlm* h, int n_tok, int n_want, int max_ctx, float* logits_
       TIMED(CLS_LINEAR, B200_TRY(linear<T>(h, ob, (long long)a.heads * a.vdim, L.a_o, mixo, W, n_tok)));
       // right: the minGRU
       const int N = b.dim;
-      TIMED(CLS_RECURRENT, B200_LAUNCH(mingru_kernel<T>, dim3(ceil_div(N, 128), h->n_entries), 128, 0, st, proj, (long long)L.ldp, L.g_z, L.g_x, L.g_g, L.zx_bias,
+      const int nw = std::min(32, std::max(1, ceil_div(h->max_entry_tokens, 8)));      // warps per CTA: segments of at least 8 tokens
+      TIMED(CLS_RECURRENT, B200_LAUNCH(mingru_kernel<T>, dim3(ceil_div(N, 32), h->n_entries), dim3(32, nw), 0, st, proj, (long long)L.ldp, L.g_z, L.g_x, L.g_g, L.zx_bias,
                                        L.zx_bias ? L.zx_bias + N : nullptr, L.gru, ob2, (long long)N, N, meta + h->off_whole_tok0, meta + h->off_whole_ntok,
                                        meta + h->off_whole_slot, meta + h->off_whole_pos0));
       TIMED(CLS_LINEAR, B200_TRY(linear<T>(h, ob2, (long long)N, L.r_o, mixo2, W, n_tok)));
@@ -2345,6 +2352,18 @@ int64_t b200_dlm_algorithmic_bytes(b200_dlm* h, int tokens, int context) {
   if (!h) return 0;
   const int64_t es = esize(h), W = h->cfg.width;
   int64_t b = h->weight_bytes - (int64_t)h->cfg.vocab * W * es;     // the embedding is gathered, not streamed
+  if (h->cfg.block == B200_BLOCK_PRE_NORM_STREAMS) {      // `tokens` = requests when decoding; the embedding table is streamed once, as the head
+    b = h->weight_bytes;
+    for (auto& L : h->layers) {
+      const b200_dlm_mixer &a = L.c.a, &m = L.c.b;
+      const int64_t per = tokens > 0 ? (int64_t)context / tokens : 0;
+      const int64_t seen = (a.window > 0 ? std::min<int64_t>(per, a.window) : per) * tokens;      // decoding: every request reads its window
+      if (L.c.mixer == B200_MIXER_LATENT_ATTENTION) b += (seen + tokens) * L.rp * es;
+      else if (L.c.mixer == B200_MIXER_PARALLEL) b += (seen + tokens) * (L.Nk + L.Nv) * es + 2 * (int64_t)tokens * m.dim * 4;
+      else b += 2 * (int64_t)tokens * a.heads * a.dim * a.vdim * 4;                                // the matrix memories, read and written
+    }
+    return b + (int64_t)tokens * W * es;
+  }
   if (h->cfg.block == B200_BLOCK_PARALLEL_RESIDUAL) {      // `tokens` = requests when decoding, as for the sandwich block
     for (auto& L : h->layers) {
       const b200_dlm_mixer& a = L.c.a;
@@ -2383,6 +2402,17 @@ int64_t b200_dlm_algorithmic_flops(b200_dlm* h, int tokens, int context) {
   const int64_t T = tokens, W = h->cfg.width;
   int64_t f = 0;
   for (auto& L : h->layers) {
+    if (h->cfg.block == B200_BLOCK_PRE_NORM_STREAMS) {
+      const b200_dlm_mixer &a = L.c.a, &m = L.c.b;
+      int64_t pairs = 0;       // (query, key) pairs of one prompt of T tokens on top of `context`
+      for (int64_t t = 0; t < T; ++t) pairs += a.window > 0 ? std::min<int64_t>(context + t + 1, a.window) : context + t + 1;
+      f += 2 * T * W * L.ncat + 2 * T * W * L.nsmall + 2 * T * W * a.heads * a.vdim;
+      if (L.c.mixer == B200_MIXER_LATENT_ATTENTION) f += 2 * T * a.heads * (a.dim + a.vdim) * a.kv_rank + 4 * pairs * a.heads * (a.kv_rank + a.rot_dims);
+      else if (L.c.mixer == B200_MIXER_PARALLEL) f += 2 * pairs * a.heads * (a.dim + a.vdim) + 2 * T * W * m.dim;
+      else f += 8 * T * a.heads * a.dim * a.vdim + 2 * T * ((int64_t)L.decay_rank * a.heads * a.dim + (int64_t)L.gate_rank * a.heads * a.vdim);
+      if (L.c.mlp != B200_MLP_NONE) f += 4 * T * W * L.c.ff;
+      continue;
+    }
     if (h->cfg.block == B200_BLOCK_PARALLEL_RESIDUAL) {
       const b200_dlm_mixer& a = L.c.a;
       f += 2 * T * W * L.ncat + 2 * T * W * L.nsmall + 2 * T * W * a.heads * a.vdim;

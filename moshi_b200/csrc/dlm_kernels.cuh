@@ -215,7 +215,7 @@ struct AttnParams {
   int cap, r, H, nsplit;
   int* err = nullptr;       // device error flags (may be null)
   // sink = null: an ordinary softmax.  window > 0: the row at position p sees keys j with 0 <= p - j < window.  gate != null:
-  // row (token, head) is multiplied by sigmoid(gate[token * ldg + head]).  (The tensor-core kernel takes none of the three.)
+  // row (token, head) is multiplied by sigmoid(gate[token * ldg + head]).
   int window = 0;
   const float* gate = nullptr;
   int ldg = 0;
@@ -440,9 +440,10 @@ __global__ void __launch_bounds__(128, 3) latent_attn_mma_kernel(AttnParams p) {
   const int row0 = p.tile_row0[tile], nrows = p.tile_rows[tile];
   const bf16* cbase = static_cast<const bf16*>(p.cache) + (long long)p.tile_slot[tile] * p.cap * R;
   const int kmax = p.tok_pos[(row0 + nrows - 1) / H];
+  const int kt_lo = p.window > 0 ? max(0, p.tok_pos[row0 / H] - p.window + 1) / KT : 0;      // the first row's window starts lowest
   const int n_kt = kmax / KT + 1;
-  const int per = (n_kt + p.nsplit - 1) / p.nsplit;
-  const int kt0 = split * per, kt1 = min(n_kt, kt0 + per);
+  const int per = (n_kt - kt_lo + p.nsplit - 1) / p.nsplit;
+  const int kt0 = kt_lo + split * per, kt1 = min(n_kt, kt0 + per);
   const int col0 = warp * SL;
 
   // query fragments of rows g and g + 8, this warp's share of the latent
@@ -467,7 +468,7 @@ __global__ void __launch_bounds__(128, 3) latent_attn_mma_kernel(AttnParams p) {
     const bool valid = orow < nrows;
     const int gr = row0 + (valid ? orow : 0);
     opos = valid ? p.tok_pos[gr / H] : -1;
-    if (valid && split == 0) { om = p.sink[gr % H]; ol = 1.f; }      // the sink: weight exp(sink) in the denominator, no value
+    if (valid && split == 0 && p.sink) { om = p.sink[gr % H]; ol = 1.f; }      // the sink: weight exp(sink) in the denominator, no value
     else { om = valid ? -INFINITY : 0.f; ol = 0.f; }
   }
   float oacc[2 * NKS][4];
@@ -535,8 +536,9 @@ __global__ void __launch_bounds__(128, 3) latent_attn_mma_kernel(AttnParams p) {
         a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
       }
       const int key = kt * KT + 4 * kq;                    // the mask also hides the zero-filled keys past the last one
-      float s0 = key <= opos ? a.x : -INFINITY, s1 = key + 1 <= opos ? a.y : -INFINITY;
-      float s2 = key + 2 <= opos ? a.z : -INFINITY, s3 = key + 3 <= opos ? a.w : -INFINITY;
+      const int klow = p.window > 0 ? opos - p.window + 1 : 0;      // the window's lower end
+      float s0 = key <= opos && key >= klow ? a.x : -INFINITY, s1 = key + 1 <= opos && key + 1 >= klow ? a.y : -INFINITY;
+      float s2 = key + 2 <= opos && key + 2 >= klow ? a.z : -INFINITY, s3 = key + 3 <= opos && key + 3 >= klow ? a.w : -INFINITY;
       float mx = fmaxf(fmaxf(s0, s1), fmaxf(s2, s3));
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
@@ -585,7 +587,7 @@ __global__ void __launch_bounds__(128, 3) latent_attn_mma_kernel(AttnParams p) {
     if (lr >= nrows) continue;
     const float mt = stat[16 + lr], lt = stat[32 + lr];
     if (p.nsplit == 1) {
-      const float inv = 1.f / lt;
+      const float inv = (p.gate ? sigmoidf(p.gate[(long long)((row0 + lr) / H) * p.ldg + (row0 + lr) % H]) : 1.f) / lt;
       float* dst = p.out + (long long)(row0 + lr) * R + col0;
 #pragma unroll
       for (int nb = 0; nb < 2 * NKS; ++nb)

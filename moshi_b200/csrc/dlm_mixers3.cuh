@@ -119,29 +119,46 @@ __global__ void __launch_bounds__(128) latent_rope_append_kernel(const T* __rest
 
 // minGRU over the step's portions: per channel S <- (1 - z) S + z c with z = sigmoid(pz + bz), c = u + 1/2 where u = px + bx >= 0
 // and sigmoid(u) below; out = S * silu(pg) -> T.  The state [slots][N] is fp32, starts from zero at position 0 and is carried
-// between steps.  A thread owns one channel of one portion and walks its tokens in order (the loads do not depend on the
-// state, only one multiply-add per token does).  Grid: (ceil(N / 128), entries).
+// between steps.  A CTA owns 32 channels of one portion; its warps cut the portion's tokens into segments that run side by
+// side: the recurrence is linear in S, so a segment's end is A S_start + B with A = prod (1 - z) and B its end from zero.  Pass 1
+// leaves (A, B) per segment, every warp folds the segments in front of it into its own start state, pass 2 walks the segment
+// again and writes the results.  Grid: (ceil(N / 32), entries), block (32, warps).
 template <typename T>
-__global__ void __launch_bounds__(128) mingru_kernel(const T* __restrict__ proj, long long ld, int off_z, int off_x, int off_g, const float* __restrict__ bz,
-                                                     const float* __restrict__ bx, float* __restrict__ state, T* __restrict__ out, long long ld_out, int N,
-                                                     const int* __restrict__ ent_tok0, const int* __restrict__ ent_ntok, const int* __restrict__ ent_slot,
-                                                     const int* __restrict__ ent_pos0) {
-  const int c = blockIdx.x * 128 + threadIdx.x, ent = blockIdx.y;
-  if (c >= N) return;
+__global__ void __launch_bounds__(1024, 1) mingru_kernel(const T* __restrict__ proj, long long ld, int off_z, int off_x, int off_g, const float* __restrict__ bz,
+                                                      const float* __restrict__ bx, float* __restrict__ state, T* __restrict__ out, long long ld_out, int N,
+                                                      const int* __restrict__ ent_tok0, const int* __restrict__ ent_ntok, const int* __restrict__ ent_slot,
+                                                      const int* __restrict__ ent_pos0) {
+  __shared__ float sa[32][32], sb[32][32];
+  const int lane = threadIdx.x, w = threadIdx.y, nw = blockDim.y, ent = blockIdx.y;
+  const int c = blockIdx.x * 32 + lane;
+  const bool live = c < N;
   const int tok0 = ent_tok0[ent], nt = ent_ntok[ent];
+  const int len = (nt + nw - 1) / nw, t0 = min(nt, w * len), t1 = min(nt, t0 + len);
+  const float bzc = live && bz ? bz[c] : 0.f, bxc = live && bx ? bx[c] : 0.f;
+  float a = 1.f, b = 0.f;
+  if (live && nw > 1) {
+    for (int i = t0; i < t1; ++i) {
+      const T* row = proj + (long long)(tok0 + i) * ld;
+      const float z = sigmoidf(to_f(row[off_z + c]) + bzc);
+      const float u = to_f(row[off_x + c]) + bxc;
+      b = fmaf(z, (u >= 0.f ? u + 0.5f : sigmoidf(u)) - b, b);
+      a *= 1.f - z;
+    }
+  }
+  sa[w][lane] = a; sb[w][lane] = b;
+  __syncthreads();
+  if (!live) return;
   float* sp = state + (long long)ent_slot[ent] * N + c;
   float S = ent_pos0[ent] > 0 ? *sp : 0.f;
-  const float bzc = bz ? bz[c] : 0.f, bxc = bx ? bx[c] : 0.f;
-#pragma unroll 4
-  for (int i = 0; i < nt; ++i) {
+  for (int u = 0; u < w; ++u) S = fmaf(sa[u][lane], S, sb[u][lane]);
+  for (int i = t0; i < t1; ++i) {
     const T* row = proj + (long long)(tok0 + i) * ld;
     const float z = sigmoidf(to_f(row[off_z + c]) + bzc);
     const float u = to_f(row[off_x + c]) + bxc;
-    const float cand = u >= 0.f ? u + 0.5f : sigmoidf(u);
-    S = fmaf(z, cand - S, S);
+    S = fmaf(z, (u >= 0.f ? u + 0.5f : sigmoidf(u)) - S, S);
     out[(long long)(tok0 + i) * ld_out + c] = from_f<T>(S * siluf(to_f(row[off_g + c])));
   }
-  *sp = S;
+  if (t1 == nt && t0 < t1) *sp = S;      // the warp that owns the portion's last token
 }
 
 // Preparation of the gated delta rule with one decay per head and key channel for matrix_memory_scan_kernel<MODE_CHDELTA>, one
