@@ -275,6 +275,7 @@ MIXERS = {"latent_attention": 1, "window_attention": 2, "gla": 3, "mlstm": 4, "p
 # layer with the tanh form of GELU, "moe_clamped_glu" routed experts with clamped gates behind a sigmoid router
 MLP_KINDS = {None: 0, "dense": 1, "moe": 2, "gated_gelu": 3, "moe_clamped_glu": 4}
 BLOCKS = {"gated_depth_average": 0, "sandwich": 1, "parallel_residual": 2, "pre_norm_streams": 3}  # block arrangement -> B200_BLOCK_*
+NO_WINDOW = 1 << 30                                                                               # a window attention without a mask: every earlier key is seen
 SINKS = {"learned": 0, "none": 1, "unit": 2}                                                      # softmax denominator's extra term -> B200_SINK_*
 ROT_PAIRINGS = {"halves": 0, "adjacent": 1}                                                       # -> B200_ROT_HALVES / B200_ROT_ADJACENT
 ROT_SCALINGS = {None: 0, "bands": 1, "ramp": 2}                                                   # -> B200_ROT_PLAIN / BANDS / RAMP
@@ -676,7 +677,8 @@ class DibulixConfig(DecoderLMConfig):
         if t == "parallel":
             l, r = m["left"], m["right"]
             a = MixerConfig(kind="window_attention", heads=int(l["heads"]), kv_heads=int(l["kv_heads"]), dim=int(l["dim"]), vdim=int(l["vdim"]),
-                            scale=float(l["scale"]), window=int((l.get("mask") or {}).get("size", 0)), bias=True, sink="unit", **_rot_fields(l, "adjacent"))
+                            scale=float(l["scale"]), window=int((l.get("mask") or {}).get("size", 0)) or NO_WINDOW, bias=True, sink="unit",
+                            **_rot_fields(l, "adjacent"))
             b = MixerConfig(kind="mingru", heads=1, dim=int(r["width"]), vdim=int(r["width"]), bias=True)
             return DecoderLayerConfig(a=a, b=b, a_scale=float(m.get("left_scale", 1.0)), b_scale=float(m.get("right_scale", 1.0)), **kw)
         a = MixerConfig(kind=t, heads=int(m["heads"]), kv_heads=int(m["kv_heads"]), dim=int(m["dim"]), vdim=int(m["vdim"]), conv=int(m["conv"]),
@@ -704,7 +706,7 @@ class DibulixConfig(DecoderLMConfig):
             rot = _rot_to_dict(a)
             if rot is not None:
                 left["rot"] = rot
-            if a.window:
+            if a.window and a.window < NO_WINDOW:
                 left["mask"] = {"size": a.window}
             mixer = {"left": left, "left_scale": L.a_scale, "right": {"width": L.b.dim}, "right_scale": L.b_scale}
         else:

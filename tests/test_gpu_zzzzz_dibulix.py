@@ -37,7 +37,9 @@ def latent(heads, dim, rot_dim, vdim, rank, scale, window, base=300.0, scaling=N
 
 
 def pair(heads, kv, dim, vdim, scale, window, width, rot_dims=0, base=1000.0, ls=1.0, rs=1.0, mlp=None):
-    left = {"dim": dim, "heads": heads, "kv_heads": kv, "mask": {"size": window}, "scale": scale, "vdim": vdim}
+    left = {"dim": dim, "heads": heads, "kv_heads": kv, "scale": scale, "vdim": vdim}
+    if window:
+        left["mask"] = {"size": window}
     if rot_dims:
         left["rot"] = {"base": base, "dims": rot_dims}
     return {"type": "parallel", "mixer": {"left": left, "left_scale": ls, "right": {"width": width}, "right_scale": rs}, "mlp": mlp}
@@ -130,6 +132,7 @@ ALONE = {
     "window_attention_alone": [pair(6, 2, 10, 12, 0.3, 13, 20, rot_dims=6, ls=1.4, rs=0.0)],
     "window_attention_all_rotated_one_kv_head": [pair(4, 1, 12, 5, 0.3, 7, 8, rot_dims=12, ls=1.0, rs=0.0)],
     "window_attention_unrotated": [pair(3, 3, 9, 9, 0.35, 30, 8, rot_dims=0, ls=1.0, rs=0.0)],
+    "window_attention_without_a_mask": [pair(4, 2, 8, 6, 0.3, 0, 8, rot_dims=8, ls=1.0, rs=0.0)],
     "mingru_alone": [pair(2, 1, 4, 4, 0.3, 3, 45, ls=0.0, rs=0.9)],
     "pair": [pair(4, 2, 8, 8, 0.3, 12, 33, rot_dims=4, ls=1.2, rs=1.1, mlp=dense(40))],
     "delta_shared_heads": [cdelta(6, 2, 9, 11, 3)],
