@@ -135,6 +135,7 @@ struct b200_dlm {
   int vmix_first = -1;                 // the first attention layer that blends values: the later ones blend its values in
   float* small32 = nullptr;            // [tokens][nsmall] fp32 results of the small projection
   float* xs = nullptr;                 // pre-norm streams block: the residual streams [tokens][streams][width]
+  float *rows3 = nullptr, *gend = nullptr;      // chunked delta rule with a decay per key channel: [tokens][heads][3 dim], [chunks][heads][dim]
   void *vfirst = nullptr, *act2 = nullptr;      // T [tokens][G * vdim] values of layer vmix_first; T [tokens * top][2 ff] experts' first product
 };
 
@@ -1209,16 +1210,16 @@ int routed_experts_glu(b200_dlm* h, const Layer& L, const T* hb, int n_tok) {
   return check_launch("grouped expert products");
 }
 
-template <int R4>
+template <int R4, bool CHD = false>
 int launch_delta_chunk(cudaStream_t st, const DeltaChunkParams& p, int n_entries) {
   constexpr int C = DELTA_CH, DP = 32 * R4;
-  const size_t smem = (size_t)((R4 <= 4 ? 2 : 1) * (2 * C * DP + C * 32 + 2 * C + 2 * C * C) + 16 * C * 32 + 3 * C * 32 + 2 * C) * sizeof(float);
+  const size_t smem = (size_t)((R4 <= 4 ? 2 : 1) * ((CHD ? 3 : 2) * C * DP + C * 32 + 2 * C + 2 * C * C) + 16 * C * 32 + 3 * C * 32 + 2 * C) * sizeof(float);
   static bool attr_set = false;
   if (!attr_set) {
-    B200_CUDA(cudaFuncSetAttribute(delta_chunk_kernel<R4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    B200_CUDA(cudaFuncSetAttribute((delta_chunk_kernel<R4, CHD>), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     attr_set = true;
   }
-  B200_LAUNCH(delta_chunk_kernel<R4>, dim3(n_entries * p.heads, ceil_div(p.vdim, 32)), 256, smem, st, p);
+  B200_LAUNCH((delta_chunk_kernel<R4, CHD>), dim3(n_entries * p.heads, ceil_div(p.vdim, 32)), 256, smem, st, p);
   return check_launch("delta_chunk");
 }
 
@@ -1244,6 +1245,29 @@ int delta_chunks(b200_dlm* h, const ScanParams& sp) {
   if (d <= 64) return launch_delta_chunk<2>(h->stream, p, h->n_entries);
   if (d <= 128) return launch_delta_chunk<4>(h->stream, p, h->n_entries);
   return launch_delta_chunk<8>(h->stream, p, h->n_entries);
+}
+
+// the same for the delta rule with a decay per key channel: the gram kernel also leaves the rows the walk multiplies the state with
+int chdelta_chunks(b200_dlm* h, const ScanParams& sp) {
+  DeltaChunkParams p;
+  p.prep = sp.prep; p.vprep = sp.vprep; p.gates = nullptr; p.prow = sp.prow; p.gram = h->gram; p.rows3 = h->rows3; p.gend = h->gend;
+  p.chunk_tok0 = h->meta_dev + h->off_chunk_tok0; p.chunk_nt = h->meta_dev + h->off_chunk_nt; p.ent_chunk0 = h->meta_dev + h->off_whole_chunk0;
+  p.ent_tok0 = h->meta_dev + h->off_whole_tok0; p.ent_ntok = h->meta_dev + h->off_whole_ntok; p.ent_slot = h->meta_dev + h->off_whole_slot;
+  p.ent_pos0 = h->meta_dev + h->off_whole_pos0;
+  p.St = sp.St; p.out = sp.out; p.heads = sp.heads; p.dim = sp.dim; p.vdim = sp.vdim;
+  const size_t gsm = (size_t)(3 * DELTA_CH * (sp.dim + 1) + DELTA_CH + DELTA_CH * DELTA_CH) * sizeof(float);
+  static bool attr_set = false;
+  if (!attr_set) {
+    B200_CUDA(cudaFuncSetAttribute(chdelta_gram_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((3 * DELTA_CH * 257 + DELTA_CH + DELTA_CH * DELTA_CH) * sizeof(float))));
+    attr_set = true;
+  }
+  B200_LAUNCH(chdelta_gram_kernel, dim3(h->n_chunks, sp.heads), 256, gsm, h->stream, p);
+  B200_TRY(check_launch("chdelta_gram"));
+  const int d = sp.dim;
+  if (d <= 32) return launch_delta_chunk<1, true>(h->stream, p, h->n_entries);
+  if (d <= 64) return launch_delta_chunk<2, true>(h->stream, p, h->n_entries);
+  if (d <= 128) return launch_delta_chunk<4, true>(h->stream, p, h->n_entries);
+  return launch_delta_chunk<8, true>(h->stream, p, h->n_entries);
 }
 
 template <typename T>
@@ -1612,10 +1636,12 @@ int step_streams(b200_dlm* h, int n_tok, int n_want, int max_ctx, float* logits_
       sp.out = h->scan32; sp.heads = a.heads; sp.dim = a.dim; sp.vdim = a.vdim;
       sp.qscale = 1.f / sqrtf((float)a.dim);
       const ScanLayout lay = scan_layout<MODE_CHDELTA>(h, sp, true);
+      const bool chunked = h->delta_chunk && h->max_entry_tokens >= 16 && h->gram != nullptr;      // prompts: chunks of tokens at once; single tokens: the scan
+      if (chunked) { sp.lpc = 0; sp.rows = 0; sp.prow = (3 * a.dim + 2 + 3) / 4 * 4; }            // plain rows, the decays as logarithms
       TIMED(CLS_RECURRENT, B200_LAUNCH(chdelta_prep_kernel, n_tok, 256, (size_t)2 * a.kv_heads * sizeof(float), st, sp, h->qkv32, a.kv_heads, L.A_log, L.dt_bias, h->gate32,
-                                       h->small32 + L.s_ba, (long long)L.nsmall);
+                                       h->small32 + L.s_ba, (long long)L.nsmall, chunked ? 1 : 0);
             B200_TRY(check_launch("chdelta_prep"));
-            B200_TRY(scan_run<MODE_CHDELTA>(h, sp, lay, true)));
+            if (chunked) B200_TRY(chdelta_chunks(h, sp)); else B200_TRY(scan_run<MODE_CHDELTA>(h, sp, lay, true)));
       const long long rows = (long long)n_tok * a.heads;
       TIMED(CLS_ELEMENTWISE, B200_LAUNCH((head_norm_gate_kernel<T, float>), (unsigned)ceil_div64(rows, 4), 128, 0, st, h->scan32, L.rnorm, 0, h->attn32, (long long)L.Nv, 0, 0, ob,
                                          a.heads, a.vdim, rows, c.norm_eps));
@@ -2046,6 +2072,14 @@ int b200_dlm_cache_begin(b200_dlm* h, int slots, int capacity, int max_step_toke
     B200_TRY(A.alloc(&h->ffo, T * W * es));
     B200_TRY(A.alloc(&h->act2, T * max_ff * es));
     h->part_floats = (size_t)600 * std::max(std::max(max_part, (size_t)16 * (max_r + 2)), (size_t)1);
+    bool any_delta = false;
+    for (auto& L : h->layers) any_delta |= L.c.mixer == B200_MIXER_CHANNEL_DELTA;
+    if (any_delta) {      // the delta rule's chunks of a step, their triangular matrices and the rows of the walk
+      h->max_chunks = max_step_tokens / DELTA_CH + std::min(slots, max_step_tokens) + 1;
+      B200_TRY(A.alloc_t(&h->gram, (size_t)h->max_chunks * max_heads * (2 * DELTA_CH + 2 * DELTA_CH * DELTA_CH)));
+      B200_TRY(A.alloc_t(&h->rows3, T * 3 * max_gate));
+      B200_TRY(A.alloc_t(&h->gend, (size_t)h->max_chunks * max_gate));
+    }
   } else if (parallel) {
     const size_t nseg = (size_t)(max_step_tokens / std::max(h->scan_seg, 8) + 2);
     B200_TRY(A.alloc_t(&h->qkv32, T * max_qkv));

@@ -563,6 +563,10 @@ struct DeltaChunkParams {
   float* St;                // [slots][heads][vdim][dim]
   float* out;               // [tokens][heads * vdim]
   int heads, dim, vdim;
+  // one decay per key channel (prep rows q | k | log g | beta): the gram kernel leaves, per token, the rows the walk multiplies the
+  // state with, rows3 [tokens][heads][3 dim] = e^(L_t) q | e^(L_t) k | e^(L_end - L_t) k, and per chunk gend [chunks][heads][dim] = e^(L_end)
+  float* rows3 = nullptr;
+  float* gend = nullptr;
 };
 
 __global__ void __launch_bounds__(256) delta_gram_kernel(DeltaChunkParams p) {
@@ -624,11 +628,12 @@ __global__ void __launch_bounds__(256) delta_gram_kernel(DeltaChunkParams p) {
 
 // A CTA owns 32 columns of one (request, head): lane = column, warp w (of 8) owns rows [w * 4 R4, (w + 1) * 4 R4) of the state in
 // registers.  Grid: (entries * heads, ceil(vdim / 32)).
-template <int R4>      // float4 groups of rows per thread: dim <= 32 R4
+template <int R4, bool CHD = false>      // float4 groups of rows per thread: dim <= 32 R4; CHD: one decay per key channel (rows3, gend)
 __global__ void __launch_bounds__(256) delta_chunk_kernel(DeltaChunkParams p) {
   constexpr int C = DELTA_CH, R = 4 * R4, NW = 8, DP = NW * R;        // rows per thread, warps, padded key size
   constexpr int NBUF = R4 <= 4 ? 2 : 1;                               // what a chunk reads is staged one chunk ahead when two buffers fit
-  constexpr int GM = 2 * C + 2 * C * C, STAGE = 2 * C * DP + C * 32 + GM;
+  constexpr int NROW = CHD ? 3 : 2;                                   // row sets per token: q, k (and the keys as the state's update takes them)
+  constexpr int GM = 2 * C + 2 * C * C, STAGE = NROW * C * DP + C * 32 + GM;
   extern __shared__ __align__(16) float csm[];
   float* wp = csm + NBUF * STAGE;      // [NW][C][32] partial K S_0
   float* op = wp + NW * C * 32;        // [NW][C][32] partial Q S_0, then [0]: e^(L_t) Q S_0
@@ -653,17 +658,21 @@ __global__ void __launch_bounds__(256) delta_chunk_kernel(DeltaChunkParams p) {
   auto stage = [&](int ck, int b) {
     float* ks = csm + b * STAGE;       // [C][DP]
     float* qs = ks + C * DP;           // [C][DP]
-    float* vs = qs + C * DP;           // [C][32]
+    float* k2 = qs + C * DP;           // CHD: [C][DP] keys decayed to the chunk's end
+    float* vs = qs + (NROW - 1) * C * DP;      // [C][32]
     float* gm = vs + C * 32;
     const int t0 = tok0 + ck * C, nt = min(C, ntok - ck * C);
     const float* gl = p.gram + ((long long)(chunk0 + ck) * heads + head) * GM;
+    const float* rows = CHD ? p.rows3 : p.prep;
+    const int rstride = CHD ? 3 * dim : p.prow;
     if (vec) {
       for (int i = threadIdx.x; i < C * (DP / 4); i += 256) {
         const int t = i / (DP / 4), d = (i - t * (DP / 4)) * 4;
         const bool ok = t < nt && d < dim;
-        const float* row = p.prep + ((long long)(t0 + (ok ? t : 0)) * heads + head) * p.prow;
+        const float* row = rows + ((long long)(t0 + (ok ? t : 0)) * heads + head) * rstride;
         cp_async_16_or_zero(qs + t * DP + d, ok ? row + d : row, ok);
         cp_async_16_or_zero(ks + t * DP + d, ok ? row + dim + d : row, ok);
+        if (CHD) cp_async_16_or_zero(k2 + t * DP + d, ok ? row + 2 * dim + d : row, ok);
       }
       for (int i = threadIdx.x; i < C * 8; i += 256) {
         const int t = i >> 3, c = blockIdx.y * 32 + (i & 7) * 4;
@@ -676,9 +685,10 @@ __global__ void __launch_bounds__(256) delta_chunk_kernel(DeltaChunkParams p) {
       for (int i = threadIdx.x; i < C * DP; i += 256) {
         const int t = i / DP, d = i - t * DP;
         const bool ok = t < nt && d < dim;
-        const float* row = p.prep + ((long long)(t0 + (ok ? t : 0)) * heads + head) * p.prow;
+        const float* row = rows + ((long long)(t0 + (ok ? t : 0)) * heads + head) * rstride;
         qs[i] = ok ? row[d] : 0.f;
         ks[i] = ok ? row[dim + d] : 0.f;
+        if (CHD) k2[i] = ok ? row[2 * dim + d] : 0.f;
       }
       for (int i = threadIdx.x; i < C * 32; i += 256) {
         const int t = i >> 5, c = blockIdx.y * 32 + (i & 31);
@@ -693,7 +703,8 @@ __global__ void __launch_bounds__(256) delta_chunk_kernel(DeltaChunkParams p) {
     const int t0 = tok0 + ck * C, nt = min(C, ntok - ck * C), buf = NBUF == 2 ? (ck & 1) : 0;
     const float* ks = csm + buf * STAGE;
     const float* qs = ks + C * DP;
-    const float* vs = qs + C * DP;
+    const float* kw = CHD ? qs + C * DP : ks;      // the keys as the state's update takes them
+    const float* vs = qs + (NROW - 1) * C * DP;
     const float* gm = vs + C * 32;
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();                   // this chunk has landed for every thread, and every thread is done with the previous one
@@ -757,15 +768,21 @@ __global__ void __launch_bounds__(256) delta_chunk_kernel(DeltaChunkParams p) {
       for (; i <= t; ++i) o0 = fmaf(P[t * C + i], us[i * 32 + lane], o0);
       if (live_col) p.out[(long long)(t0 + t) * heads * vdim + head * vdim + col] = (o0 + o1) + (o2 + o3);
     }
-    const float gall = expf(gm[nt - 1]);
+    if (CHD) {      // every row of the state has its own decay over the chunk (the gram kernel leaves L = 0: the factors above are 1)
+      const float* ge = p.gend + ((long long)(chunk0 + ck) * heads + head) * dim;
 #pragma unroll
-    for (int i = 0; i < R; ++i) S[i] *= gall;
+      for (int i = 0; i < R; ++i) S[i] *= row0 + i < dim ? __ldg(ge + row0 + i) : 0.f;
+    } else {
+      const float gall = expf(gm[nt - 1]);
+#pragma unroll
+      for (int i = 0; i < R; ++i) S[i] *= gall;
+    }
 #pragma unroll 4
     for (int t = 0; t < nt; ++t) {
       const float w = uw[t * 32 + lane];
 #pragma unroll
       for (int j = 0; j < R4; ++j) {
-        const float4 k4 = *reinterpret_cast<const float4*>(ks + t * DP + row0 + 4 * j);
+        const float4 k4 = *reinterpret_cast<const float4*>(kw + t * DP + row0 + 4 * j);
         S[4 * j] = fmaf(k4.x, w, S[4 * j]); S[4 * j + 1] = fmaf(k4.y, w, S[4 * j + 1]); S[4 * j + 2] = fmaf(k4.z, w, S[4 * j + 2]); S[4 * j + 3] = fmaf(k4.w, w, S[4 * j + 3]);
       }
     }

@@ -137,7 +137,8 @@ __global__ void __launch_bounds__(1024, 1) mingru_kernel(const T* __restrict__ p
   const float bzc = live && bz ? bz[c] : 0.f, bxc = live && bx ? bx[c] : 0.f;
   float a = 1.f, b = 0.f;
   if (live && nw > 1) {
-    for (int i = t0; i < t1; ++i) {
+#pragma unroll 4
+    for (int i = t0; i < t1; ++i) {      // the loads do not depend on the state: four tokens' worth are in flight
       const T* row = proj + (long long)(tok0 + i) * ld;
       const float z = sigmoidf(to_f(row[off_z + c]) + bzc);
       const float u = to_f(row[off_x + c]) + bxc;
@@ -151,6 +152,7 @@ __global__ void __launch_bounds__(1024, 1) mingru_kernel(const T* __restrict__ p
   float* sp = state + (long long)ent_slot[ent] * N + c;
   float S = ent_pos0[ent] > 0 ? *sp : 0.f;
   for (int u = 0; u < w; ++u) S = fmaf(sa[u][lane], S, sb[u][lane]);
+#pragma unroll 4
   for (int i = t0; i < t1; ++i) {
     const T* row = proj + (long long)(tok0 + i) * ld;
     const float z = sigmoidf(to_f(row[off_z + c]) + bzc);
@@ -169,7 +171,7 @@ __global__ void __launch_bounds__(1024, 1) mingru_kernel(const T* __restrict__ p
 // prep row of (token, head): [q | k | g | beta] (plain or lane-ordered, as scan_prep_kernel lays rows out).
 __global__ void __launch_bounds__(256) chdelta_prep_kernel(ScanParams p, const float* __restrict__ conv, int G, const float* __restrict__ A_log,
                                                            const float* __restrict__ dt_bias, const float* __restrict__ za, const float* __restrict__ zb,
-                                                           long long ldzb) {
+                                                           long long ldzb, int store_log) {      // store_log: log g instead of g (the chunked form sums them)
   extern __shared__ float rinv[];       // [2 * G] inverse lengths of the q and k heads
   const long long t = blockIdx.x;
   const int heads = p.heads, dim = p.dim, vdim = p.vdim, rep = heads / G;
@@ -193,10 +195,89 @@ __global__ void __launch_bounds__(256) chdelta_prep_kernel(ScanParams p, const f
     const bool live = d < dim;
     o[at] = live ? siluf(c[g * dim + d]) * rinv[g] * p.qscale : 0.f;
     o[Dp + at] = live ? siluf(c[(G + g) * dim + d]) * rinv[G + g] : 0.f;
-    o[2 * Dp + at] = live ? expf(-expf(A_log[h]) * softplusf(za[t * heads * dim + h * dim + d] + dt_bias[h * dim + d])) : 0.f;
+    const float lg = live ? -expf(A_log[h]) * softplusf(za[t * heads * dim + h * dim + d] + dt_bias[h * dim + d]) : 0.f;
+    o[2 * Dp + at] = store_log ? lg : (live ? expf(lg) : 0.f);
   }
   for (int h = threadIdx.x; h < heads; h += 256) dst[h * p.prow + 3 * Dp] = sigmoidf(zb[t * ldzb + h]);
   for (int i = threadIdx.x; i < heads * vdim; i += 256) p.vprep[t * heads * vdim + i] = siluf(c[2 * G * dim + i]);
+}
+
+// The chunked delta rule (dlm_mixers2.cuh) with one decay per key channel.  With L_t[d] the chunk's running sum of log g[d]:
+//   A[t][i] = beta_t sum_d k_t[d] k_i[d] e^(L_t[d] - L_i[d])  (i < t),    P[t][i] = sum_d q_t[d] k_i[d] e^(L_t[d] - L_i[d])  (i <= t)
+//   b_t = beta_t (v_t - S_0^T (e^(L_t) k_t)),  o_t = S_0^T (e^(L_t) q_t) + sum_i P[t][i] u_i,  S_end = e^(L_end) S_0 + sum_t (e^(L_end - L_t) k_t) u_t^T
+// so the walk is the scalar one on three row sets per token (rows3) with unit scalar factors, and a decay per state row at the
+// chunk's end (gend).  Every exponent is <= 0.  One CTA per (chunk, head), off the chain; prep rows are plain: q | k | log g | beta.
+__global__ void __launch_bounds__(256) chdelta_gram_kernel(DeltaChunkParams p) {
+  constexpr int C = DELTA_CH;
+  extern __shared__ float gsm[];
+  const int ck = blockIdx.x, head = blockIdx.y, dim = p.dim, DS = dim + 1;
+  float* ks = gsm;                     // [C][DS]
+  float* qs = ks + C * DS;             // [C][DS]
+  float* Ls = qs + C * DS;             // [C][DS] running sums of log g
+  float* be = Ls + C * DS;             // [C]
+  float* As = be + C;                  // [C][C]
+  const int tok0 = p.chunk_tok0[ck], nt = p.chunk_nt[ck];
+  for (int i = threadIdx.x; i < C * dim; i += 256) {
+    const int t = i / dim, d = i - t * dim;
+    const float* row = p.prep + ((long long)(tok0 + t) * p.heads + head) * p.prow;
+    qs[t * DS + d] = t < nt ? row[d] : 0.f;
+    ks[t * DS + d] = t < nt ? row[dim + d] : 0.f;
+    Ls[t * DS + d] = t < nt ? row[2 * dim + d] : 0.f;
+  }
+  if (threadIdx.x < C) be[threadIdx.x] = threadIdx.x < nt ? p.prep[((long long)(tok0 + threadIdx.x) * p.heads + head) * p.prow + 3 * dim] : 0.f;
+  __syncthreads();
+  for (int d = threadIdx.x; d < dim; d += 256) {
+    float acc = 0.f;
+    for (int t = 0; t < C; ++t) { acc += Ls[t * DS + d]; Ls[t * DS + d] = acc; }
+  }
+  __syncthreads();
+  float* g = p.gram + ((long long)ck * p.heads + head) * (2 * C + 2 * C * C);
+  if (threadIdx.x < C) { g[threadIdx.x] = 0.f; g[C + threadIdx.x] = be[threadIdx.x]; }      // no scalar decay: the walk's e^(L) factors are 1
+  g += C;
+  // the rows the walk takes, and the state's decay over the chunk
+  for (int i = threadIdx.x; i < nt * dim; i += 256) {
+    const int t = i / dim, d = i - t * dim;
+    const float lt = Ls[t * DS + d], e = expf(lt);
+    float* r3 = p.rows3 + ((long long)(tok0 + t) * p.heads + head) * 3 * dim;
+    r3[d] = e * qs[t * DS + d];
+    r3[dim + d] = e * ks[t * DS + d];
+    r3[2 * dim + d] = expf(Ls[(nt - 1) * DS + d] - lt) * ks[t * DS + d];
+  }
+  for (int d = threadIdx.x; d < dim; d += 256) p.gend[((long long)ck * p.heads + head) * dim + d] = expf(Ls[(nt - 1) * DS + d]);
+  for (int i = threadIdx.x; i < C * C; i += 256) {
+    const int t = i / C, j = i - t * C;
+    float a = 0.f, pq = 0.f;
+    if (j <= t && t < nt) {
+      float kk = 0.f, kq = 0.f;
+      if (j == t) {
+        for (int d = 0; d < dim; ++d) kq = fmaf(ks[j * DS + d], qs[t * DS + d], kq);
+      } else {
+        for (int d = 0; d < dim; ++d) {
+          const float kd = ks[j * DS + d] * expf(Ls[t * DS + d] - Ls[j * DS + d]);
+          kk = fmaf(ks[t * DS + d], kd, kk);
+          kq = fmaf(qs[t * DS + d], kd, kq);
+        }
+      }
+      pq = kq;
+      if (j < t) a = be[t] * kk;
+    }
+    As[i] = a;
+    g[C + C * C + i] = pq;
+  }
+  __syncthreads();
+  // T = (I + A)^-1, unit lower triangular: lane j of warp 0 solves (I + A) x = e_j by forward substitution
+  if (threadIdx.x < C) {
+    const int j = threadIdx.x;
+    float x[C];
+#pragma unroll
+    for (int t = 0; t < C; ++t) {
+      float acc = t == j ? 1.f : 0.f;
+#pragma unroll
+      for (int i = 0; i < t; ++i) acc = fmaf(-As[t * C + i], x[i], acc);
+      x[t] = acc;
+      g[C + t * C + j] = acc;
+    }
+  }
 }
 
 // rows of logits times a constant: bf16 rows with a padded stride (in_bf given) or fp32 in place -> fp32 [rows][V]

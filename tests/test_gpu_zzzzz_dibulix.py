@@ -360,3 +360,29 @@ def test_configurations_drawn_from_the_designs_space(seed):
             assert_close(gen.step([(0, toks)], list(range(80))), want, dtype, "whole")
             assert_close(in_portions(gen, 1, toks, [37] + [1] * 20 + [2, 5, 2]), want, dtype, "portions")
             assert gen.error_flags() == 0
+
+
+@pytest.mark.parametrize("dim,vdim,heads,kv", [(9, 11, 4, 2), (17, 6, 2, 2), (40, 33, 2, 1), (64, 64, 3, 3), (128, 32, 2, 2), (200, 16, 1, 1)])
+def test_delta_rule_in_chunks_against_the_oracle_and_the_token_by_token_kernel(dim, vdim, heads, kv):
+    """Portions of at least 16 tokens run in chunks of 32 (every register layout of the chunk kernel), shorter ones token by token:
+    ragged last chunks, portions on a carried state, a mixed batch, and decays from next to one down to a tenth per token."""
+    cfg = make_cfg([cdelta(heads, kv, dim, vdim, 3)], vocab=59, width=40, streams=2, ranks=(6, 6))
+
+    def edit(t):
+        a = t["l0.mix.A_log"].float()
+        t["l0.mix.A_log"] = torch.linspace(-6.0, 1.0, a.numel()).to(t["l0.mix.A_log"].dtype)      # per head: g from ~1 to ~e^-2.7 per token
+    model, orc = build(cfg, torch.float32, seed=21, edit=edit)
+    a, b = tokens(150, cfg.vocab, 30), tokens(47, cfg.vocab, 31)
+    wa, wb = orc.forward(a), orc.forward(b)
+    with gen_for(model) as gen:
+        got = in_portions(gen, 0, a, [70, 33, 5, 17])                                        # chunks, a ragged chunk, the scan, a short chunk, the rest
+        assert_close(got, wa, torch.float32, "chunks on a carried state")
+        gen.release(0)
+        gen.step([(0, a[:100]), (1, b[:20])], [])
+        got = gen.step([(1, b[20:]), (0, a[100:])], list(range(27 + 50)))                    # two requests of unequal length in one step
+        assert_close(got[:27], wb[20:], torch.float32, "batch b")
+        assert_close(got[27:], wa[100:], torch.float32, "batch a")
+        gen.release(0)
+        gen.set_option("delta_chunk", 0)
+        assert_close(gen.step([(0, a)], list(range(150))), wa, torch.float32, "token by token")
+        gen.set_option("delta_chunk", 1)
