@@ -163,7 +163,7 @@ def sharpen(names, by):
     return edit
 
 
-@pytest.mark.parametrize("window", [1, 2, 7, 32, 33, 40])
+@pytest.mark.parametrize("window", [1, 2, 7, 32, 33, 40, 97, 128])
 @pytest.mark.parametrize("kind", ["window", "latent"])
 def test_sharp_attention_at_the_windows_edges(kind, window):
     """Large query and key weights make single keys dominate, so a window that is one token off shows; the oracle itself moves by
@@ -174,7 +174,8 @@ def test_sharp_attention_at_the_windows_edges(kind, window):
         layers, names = [latent(3, 8, 4, 8, 12, 0.5, window)], ("mix.q", "mix.uk", "mix.dkv")
     cfg = make_cfg(layers, vocab=53, width=40, streams=2)
     model, orc = build(cfg, torch.float32, seed=5, edit=sharpen(names, 3.0))
-    toks = tokens(100, cfg.vocab, 3)
+    n = max(100, 2 * window + 36)                      # the window passes over prompt tokens and over single tokens
+    toks = tokens(n, cfg.vocab, 3)
     want = orc.forward(toks)
     for off in (-1, 1):
         if window + off < 1:
@@ -184,11 +185,33 @@ def test_sharp_attention_at_the_windows_edges(kind, window):
         (m["left"] if kind == "window" else m)["mask"]["size"] = window + off
         other = Oracle(d, orc.t).forward(toks)
         assert float(logit_error(other, want).max()) > 50 * TOL[torch.float32]
-    with gen_for(model) as gen:
-        assert_close(gen.step([(0, toks)], list(range(100))), want, torch.float32, "whole")
+    with gen_for(model, capacity=n + 8, max_step_tokens=max(256, n)) as gen:
+        assert_close(gen.step([(0, toks)], list(range(n))), want, torch.float32, "whole")
         gen.release(0)
-        got = in_portions(gen, 0, toks, [window + 1, 2, 3] + [1] * 40 + [2] * 5)
+        got = in_portions(gen, 0, toks, [window + 1, 2, 3] + [1] * (window + 8 if window > 40 else 40) + [2] * 5)
         assert_close(got, want, torch.float32, "portions and single tokens")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("kind", ["window", "latent"])
+def test_a_far_key_without_a_mask(kind, dtype):
+    """Without a mask every earlier key is seen: sharp scores over 600 tokens, so that single keys hundreds of positions back carry
+    rows of the result, in a prompt whose keys are cut over CTAs, in portions, and in single tokens."""
+    if kind == "window":
+        layers, names = [pair(4, 2, 16, 16, 0.5, 0, 8, rot_dims=8, ls=1.0, rs=0.0)], ("left.q", "left.k")
+    else:
+        layers, names = [latent(2, 16, 16, 16, 16, 0.5, 0)], ("mix.q", "mix.uk", "mix.dkv")
+    cfg = make_cfg(layers, vocab=53, width=48, streams=2)
+    model, orc = build(cfg, dtype, seed=6, edit=sharpen(names, 3.0))
+    toks = tokens(600, cfg.vocab, 5)
+    want = orc.forward(toks)
+    short = orc.forward(toks[300:])                        # the same last tokens without the first 300: the far keys matter
+    assert float(logit_error(short[-40:], want[-40:]).max()) > 50 * TOL[torch.float32]
+    with gen_for(model, capacity=640, max_step_tokens=640) as gen:
+        assert_close(gen.step([(0, toks)], list(range(600))), want, dtype, "whole")
+        gen.release(0)
+        got = in_portions(gen, 0, toks, [517, 2, 33] + [1] * 40)
+        assert_close(got, want, dtype, "portions and single tokens")
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
