@@ -916,16 +916,16 @@ def _dibulix_cfgs(size: str) -> dict:
     W, kinds, H, G, d, rd, r, win, Hr, dk, dv, N, ff, V, S = DIBULIX_SIZES[size]
     ramp = {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}
     mix = {
-        "latent_attention": {"dim": d, "heads": H, "kv_rank": r, "mask": {"size": win}, "rot_dim": rd, "rot": {"base": 1e6, "dims": rd, "scaling": ramp},
+        "latent_attention": {"dim": d, "heads": H, "kv_rank": r, "mask": {"size": win}, "rot_dim": rd, "rot": {"base": 1e5, "dims": rd, "scaling": ramp},
                              "scale": (d + rd) ** -0.5, "vdim": d},
-        "parallel": {"left": {"dim": d, "heads": H, "kv_heads": G, "mask": {"size": win}, "rot": {"base": 5e5, "dims": d // 2}, "scale": d ** -0.5, "vdim": d},
-                     "left_scale": 1.2, "right": {"width": N}, "right_scale": 1.1},
+        "parallel": {"left": {"dim": d, "heads": H, "kv_heads": G, "mask": {"size": win}, "rot": {"base": 1e4, "dims": d // 2}, "scale": d ** -0.5, "vdim": d},
+                     "left_scale": 1.0, "right": {"width": N}, "right_scale": 0.5},
         "channel_delta": {"conv": 4, "dim": dk, "heads": Hr, "kv_heads": Hr, "vdim": dv},
     }
     dense = {"ff": ff, "kind": "dense"}
 
     def dib(layer_kinds, mlps):
-        cfg = DecoderLMConfig.from_dict({"architecture": "Dibulix", "logit_scale": 0.25, "norm": {"eps": 1e-6}, "streams": S, "vocab": V, "width": W,
+        cfg = DecoderLMConfig.from_dict({"architecture": "Dibulix", "logit_scale": 0.5, "norm": {"eps": 1e-6}, "streams": S, "vocab": V, "width": W,
                                          "layers": [{"type": k, "mixer": mix[k], "mlp": m} for k, m in zip(layer_kinds, mlps)]})
         for L in cfg.layers:
             if L.type == "channel_delta":

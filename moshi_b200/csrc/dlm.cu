@@ -259,9 +259,12 @@ int launch_attn(cudaStream_t st, const AttnParams& p, int tiles, int nsplit) {
 // keys are cut over `nsplit` CTAs per tile when the tiles alone cannot fill the GPU (decoding, short portions)
 int pick_split(int forced, int tiles, int max_ctx, int rpt, int r, size_t part_floats) {
   const int key_tiles = ceil_div(max_ctx, 32);
+  // one wave: registers allow three CTAs of the tensor-core kernel per SM, its two key tiles of rows of r elements may allow fewer
+  const size_t cta_smem = (size_t)2 * 32 * (r + 8) * 2 + 11 * 1024;
+  const int per_sm = (int)std::max<size_t>(1, std::min<size_t>(3, (size_t)227 * 1024 / cta_smem));
   int nsplit = 1;
   if (forced > 0) nsplit = std::min(forced, 64);
-  else if (tiles < 148) nsplit = std::min(std::max(444 / tiles, 1), 64);      // one wave of three CTAs per SM
+  else if (tiles < 148) nsplit = std::min(std::max(148 * per_sm / tiles, 1), 64);
   nsplit = std::max(1, std::min(nsplit, key_tiles));
   nsplit = ceil_div(key_tiles, ceil_div(key_tiles, nsplit));                   // no split without a key tile
   while (nsplit > 1 && (size_t)tiles * nsplit * rpt * (r + 2) > part_floats) --nsplit;

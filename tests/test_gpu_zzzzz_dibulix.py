@@ -74,7 +74,7 @@ ODD = make_cfg([cdelta(4, 2, 9, 11, 3, mlp=dense(30)),
                 pair(4, 4, 14, 5, 0.2, 9, 19, rot_dims=14, ls=0.7, rs=1.2, mlp=dense(13))], vocab=97, width=52, streams=3)
 # aligned sizes: in bfloat16 every linear takes the tcgen05 GEMM and the window attention its tensor-core kernel; a layer order that
 # starts with attention; one key head for all query heads; a delta rule whose query/key heads serve two value heads each
-ALIGNED = make_cfg([pair(4, 1, 32, 16, 0.18, 48, 128, rot_dims=16, ls=1.2, rs=1.1, mlp=dense(128)),
+ALIGNED = make_cfg([pair(4, 1, 32, 16, 0.18, 48, 128, rot_dims=16, ls=1.25, rs=0.9, mlp=dense(128)),
                     latent(4, 32, 16, 32, 48, 0.15, 64, scaling={"factor": 8.0, "original": 64, "fast": 16.0, "slow": 1.0}, mlp=dense(64)),
                     cdelta(4, 2, 16, 32, 4),
                     pair(8, 2, 16, 16, 0.25, 33, 64, rot_dims=8),
@@ -134,7 +134,7 @@ ALONE = {
     "window_attention_unrotated": [pair(3, 3, 9, 9, 0.35, 30, 8, rot_dims=0, ls=1.0, rs=0.0)],
     "window_attention_without_a_mask": [pair(4, 2, 8, 6, 0.3, 0, 8, rot_dims=8, ls=1.0, rs=0.0)],
     "mingru_alone": [pair(2, 1, 4, 4, 0.3, 3, 45, ls=0.0, rs=0.9)],
-    "pair": [pair(4, 2, 8, 8, 0.3, 12, 33, rot_dims=4, ls=1.2, rs=1.1, mlp=dense(40))],
+    "pair": [pair(4, 2, 8, 8, 0.3, 12, 33, rot_dims=4, ls=0.85, rs=1.3, mlp=dense(40))],
     "delta_shared_heads": [cdelta(6, 2, 9, 11, 3)],
     "delta_one_tap": [cdelta(2, 2, 17, 6, 1)],
     "delta_five_taps_one_head": [cdelta(1, 1, 33, 20, 5, mlp=dense(16))],
@@ -202,7 +202,8 @@ def test_a_far_key_without_a_mask(kind, dtype):
     else:
         layers, names = [latent(2, 16, 16, 16, 16, 0.5, 0)], ("mix.q", "mix.uk", "mix.dkv")
     cfg = make_cfg(layers, vocab=53, width=48, streams=2)
-    model, orc = build(cfg, dtype, seed=6, edit=sharpen(names, 3.0))
+    # bfloat16 rounds keys and queries: scores as sharp as float32 can take would turn that rounding into the result's error
+    model, orc = build(cfg, dtype, seed=6, edit=sharpen(names, 3.0 if dtype == torch.float32 else 1.6))
     toks = tokens(600, cfg.vocab, 5)
     want = orc.forward(toks)
     short = orc.forward(toks[300:])                        # the same last tokens without the first 300: the far keys matter
