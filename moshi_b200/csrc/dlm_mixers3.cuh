@@ -137,8 +137,8 @@ __global__ void __launch_bounds__(1024, 1) mingru_kernel(const T* __restrict__ p
   const float bzc = live && bz ? bz[c] : 0.f, bxc = live && bx ? bx[c] : 0.f;
   float a = 1.f, b = 0.f;
   if (live && nw > 1) {
-#pragma unroll 4
-    for (int i = t0; i < t1; ++i) {      // the loads do not depend on the state: four tokens' worth are in flight
+#pragma unroll 8
+    for (int i = t0; i < t1; ++i) {      // the loads do not depend on the state: eight tokens' worth are in flight
       const T* row = proj + (long long)(tok0 + i) * ld;
       const float z = sigmoidf(to_f(row[off_z + c]) + bzc);
       const float u = to_f(row[off_x + c]) + bxc;
@@ -152,7 +152,7 @@ __global__ void __launch_bounds__(1024, 1) mingru_kernel(const T* __restrict__ p
   float* sp = state + (long long)ent_slot[ent] * N + c;
   float S = ent_pos0[ent] > 0 ? *sp : 0.f;
   for (int u = 0; u < w; ++u) S = fmaf(sa[u][lane], S, sb[u][lane]);
-#pragma unroll 4
+#pragma unroll 8
   for (int i = t0; i < t1; ++i) {
     const T* row = proj + (long long)(tok0 + i) * ld;
     const float z = sigmoidf(to_f(row[off_z + c]) + bzc);
