@@ -138,7 +138,7 @@ __global__ void __launch_bounds__(1024, 1) mingru_kernel(const T* __restrict__ p
   float a = 1.f, b = 0.f;
   if (live && nw > 1) {
 #pragma unroll 8
-    for (int i = t0; i < t1; ++i) {      // the loads do not depend on the state: eight tokens' worth are in flight
+    for (int i = t0; i < t1; ++i) {      // the loads do not depend on the state, so several tokens' loads may be in flight at once
       const T* row = proj + (long long)(tok0 + i) * ld;
       const float z = sigmoidf(to_f(row[off_z + c]) + bzc);
       const float u = to_f(row[off_x + c]) + bxc;
