@@ -410,3 +410,47 @@ def test_delta_rule_in_chunks_against_the_oracle_and_the_token_by_token_kernel(d
         gen.set_option("delta_chunk", 0)
         assert_close(gen.step([(0, a)], list(range(150))), wa, torch.float32, "token by token")
         gen.set_option("delta_chunk", 1)
+
+
+def drawn_small_model(seed):
+    """Layer sizes of a small real model (widths of 128 to 384, heads of 32 to 128, windows of 48 to 257): every mixer kind at least once."""
+    g = torch.Generator().manual_seed(seed)
+
+    def pick(*xs):
+        return xs[int(torch.randint(0, len(xs), (1,), generator=g))]
+
+    def mlp():
+        return pick(None, dense(pick(256, 320, 200)))
+    kinds = ["latent", "pair", "delta"] + [pick("latent", "pair", "delta") for _ in range(pick(1, 2))]
+    layers = []
+    for i in torch.randperm(len(kinds), generator=g).tolist():
+        if kinds[i] == "latent":
+            rd = pick(16, 32, 64, 8)
+            layers.append(latent(pick(2, 4, 8, 6), pick(32, 64, 96, 48), rd, pick(32, 64, 48), pick(64, 128, 192, 96), pick(0.1, 0.125), pick(0, 64, 100, 257),
+                                 base=pick(1e4, 1e6), scaling=pick(None, {"factor": pick(4.0, 8.0), "original": pick(256, 1024), "fast": pick(32.0, 16.0), "slow": pick(1.0, 2.0)}),
+                                 mlp=mlp()))
+        elif kinds[i] == "pair":
+            kv, dim = pick(1, 2, 4), pick(32, 64, 96, 128, 48)
+            layers.append(pair(kv * pick(1, 2, 4), kv, dim, pick(32, 64, 96, 48), pick(0.1, 0.125), pick(0, 48, 130, 256), pick(128, 384, 200),
+                               rot_dims=pick(0, 16, 24, dim), base=pick(1e4, 5e5), ls=pick(1.0, 1.3, 0.8), rs=pick(1.0, 0.9), mlp=mlp()))
+        else:
+            kv = pick(1, 2, 3, 4)
+            layers.append(cdelta(kv * pick(1, 2), kv, pick(32, 48, 64, 128), pick(32, 64, 128, 48), pick(2, 3, 4), mlp=mlp()))
+    return make_cfg(layers, vocab=pick(320, 1000, 777), width=pick(128, 160, 256, 320, 384, 200), streams=pick(None, 1, 2, 3, 4), logit_scale=pick(0.3, 0.5, 1.0),
+                    eps=pick(1e-5, 1e-6), ranks=(pick(16, 24, 32), pick(16, 24, 32)))
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_drawn_models_at_a_small_models_sizes(seed):
+    """Whole prompt, prompt + single tokens, and ragged portions with chunk-sized and two-token pieces, in both precisions."""
+    cfg = drawn_small_model(40 + seed)
+    toks = tokens(330, cfg.vocab, 60 + seed)
+    for dtype in (torch.float32, torch.bfloat16):
+        model, orc = build(cfg, dtype, seed=seed)
+        want = orc.forward(toks)
+        with gen_for(model, capacity=340, max_step_tokens=340) as gen:
+            assert_close(gen.step([(0, toks)], list(range(330))), want, dtype, "whole")
+            assert_close(in_portions(gen, 1, toks, [290] + [1] * 40), want, dtype, "prompt and single tokens")
+            gen.release(1)
+            assert_close(in_portions(gen, 1, toks, [2, 3, 17, 97, 2, 33, 64, 5, 31, 2, 16] + [1] * 20), want, dtype, "portions")
+            assert gen.error_flags() == 0
