@@ -386,7 +386,7 @@ int b200_frame_read_buffer(b200_frame* f, const char* name, void* dst_dev, int64
  *           c = u + 1/2 where u = W_x h + b_x >= 0 and sigmoid(u) below; the result is W_o (S * silu(W_g h))
  *           B200_MIXER_CHANNEL_DELTA: B200_MIXER_DELTA with one decay per head and key channel,
  *           g = exp(-exp(A_log[h]) softplus(W_a2 (W_a1 h) + dt_bias)), acting on the rows of S, and the gate
- *           sigmoid(W_g2 (W_g1 h)) on the normed result; single tokens and portions run token by token
+ *           sigmoid(W_g2 (W_g1 h)) on the normed result; portions of at least 16 tokens run in chunks of 32, the rest token by token
  *   mlp     B200_MLP_DENSE_RELU2 on its own norm
  * Precision: compute_dtype B200_BF16 = bf16 weights / activations / cache with fp32 accumulation, while norms, attention
  * scores and weights, gates, routers, recurrent state, the residual stream and the depth average stay fp32; B200_F32 =
